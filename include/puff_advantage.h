@@ -1,0 +1,141 @@
+/*
+ * C ABI of the sm_100a advantage library (libpuff_advantage_sm100.so).
+ *
+ * Plain pointers and sizes only: no torch types, no C++ types, no exceptions.
+ * Every entry point returns 0 on success, a negative PUFF_ERR_* code when an
+ * argument is rejected before anything is launched, or a positive cudaError_t
+ * value when the CUDA runtime reports a failure.  Nothing here falls back to
+ * the CPU: without an sm_100 device every launch returns an error.
+ *
+ * The recurrence (one [horizon] row per segment, walked backwards, A starts 0):
+ *     nn    = 1 - dones[t+1]
+ *     rho   = min(importance[t], rho_clip);   c = min(importance[t], c_clip)
+ *     delta = rho * (rewards[t+1] + gamma*values[t+1]*nn - values[t])
+ *     A     = delta + gamma*lambda*c*A*nn;     advantages[t] = A
+ * for t = horizon-2 ... 0.  advantages[:, horizon-1] is never written.
+ */
+#ifndef PUFF_ADVANTAGE_H_
+#define PUFF_ADVANTAGE_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error codes (negative: rejected before launch) ---------------------- */
+#define PUFF_OK                 0
+#define PUFF_ERR_NULL          -1   /* a required pointer is NULL                 */
+#define PUFF_ERR_SHAPE         -2   /* negative num_segments / horizon            */
+#define PUFF_ERR_VARIANT       -3   /* unknown variant                            */
+#define PUFF_ERR_ALIGN         -4   /* a pointer is not 4-byte aligned            */
+#define PUFF_ERR_ALIAS         -5   /* advantages / seg_abs_sum overlap an input  */
+#define PUFF_ERR_ARCH          -6   /* current device is not compute capability 10.x */
+#define PUFF_ERR_DRIVER        -7   /* cuTensorMapEncodeTiled unavailable / failed */
+#define PUFF_ERR_DEVICE_WAIT   -8   /* a bounded in-kernel wait gave up (see _device_status) */
+#define PUFF_ERR_WORKSPACE     -9   /* scratch / workspace too small or missing   */
+#define PUFF_ERR_SIZE         -10   /* size beyond what the entry point supports  */
+
+/* ---- kernel variants ----------------------------------------------------- */
+#define PUFF_VARIANT_AUTO       0   /* pick from (num_segments, horizon, alignment)            */
+#define PUFF_VARIANT_SERIAL     1   /* one thread per row, reference operation order: bit-exact */
+#define PUFF_VARIANT_SCAN       2   /* affine-pair scan along the horizon: |a-b| <= max(1e-6, 1e-5|b|) */
+#define PUFF_VARIANT_GENERIC    3   /* serial, direct global loads; any alignment, any horizon  */
+
+/* Kernel actually used by the last launch of the calling thread (tests/bench). */
+#define PUFF_KERNEL_NONE        0
+#define PUFF_KERNEL_TMA2D       1   /* serial, 2-D TMA tiles, 128B-swizzled shared memory */
+#define PUFF_KERNEL_BULK1D      2   /* serial, 1-D bulk-copied dense row tiles             */
+#define PUFF_KERNEL_SCAN        3
+#define PUFF_KERNEL_GENERIC     4
+
+/*
+ * The advantage op on DEVICE buffers, asynchronous on `cuda_stream`.
+ *
+ * Replaces the reference launcher compute_puff_advantage_cuda
+ * (pufferlib/extensions/cuda/pufferlib.cu:53-82) and its kernel
+ * puff_advantage_kernel (cu:41-51) / puff_advantage_row_cuda (cu:7-20);
+ * argument meaning follows cu:53-55 with gamma..c_clip already narrowed to
+ * float as at cu:70-73.  All five arrays are row-major contiguous
+ * [num_segments, horizon] fp32 on the current device.
+ *
+ * seg_abs_sum (nullable, [num_segments] fp32, device): when non-NULL the same
+ * kernel also writes sum_t |advantages[s, t]| over t = 0..horizon-2, the
+ * quantity `advantages.abs().sum(axis=1)` of pufferl.py:359 computes from a
+ * zero-initialised buffer.
+ *
+ * Differences from the reference launcher, all deliberate: runs on the
+ * caller's stream instead of the legacy default stream (cu:64); 64-bit
+ * offsets (cu:48 overflows int at 2^31 elements); num_segments == 0 or
+ * horizon < 2 return PUFF_OK without a launch (cu:62 launches a 0-block grid,
+ * which is a CUDA error); no allocation, no host synchronisation.
+ */
+int puff_advantage_sm100_launch(const float* values, const float* rewards,
+                                const float* dones, const float* importance,
+                                float* advantages, float* seg_abs_sum,
+                                float gamma, float lambda, float rho_clip, float c_clip,
+                                long long num_segments, long long horizon,
+                                int variant, void* cuda_stream);
+
+/*
+ * The same op on HOST buffers (pinned memory recommended), synchronous.
+ *
+ * Stands where the reference's host-tensor path stands: the Python wrapper's
+ * `.cpu()` route (pufferl.py:666-678) and compute_puff_advantage_cpu
+ * (pufferlib/extensions/pufferlib.cpp:75-85), i.e. "the caller holds host
+ * memory".  Rows are cut into blocks that are copied in, processed and copied
+ * out on rotating streams so that both PCIe directions and the kernel overlap.
+ * h_advantages[:, horizon-1] is left untouched.  The device staging workspace
+ * is allocated on first use and cached per device; puff_advantage_sm100_host_release
+ * frees it.  Bytes moved: 16*S*H host->device, 4*S*(H-1) (+4*S) device->host.
+ */
+int puff_advantage_sm100_host(const float* h_values, const float* h_rewards,
+                              const float* h_dones, const float* h_importance,
+                              float* h_advantages, float* h_seg_abs_sum,
+                              float gamma, float lambda, float rho_clip, float c_clip,
+                              long long num_segments, long long horizon,
+                              int variant, int device);
+int puff_advantage_sm100_host_release(int device);
+
+/*
+ * Prioritised-replay weights from the fused per-segment sums, on DEVICE
+ * buffers, asynchronous on `cuda_stream`.  Replaces the eager torch sequence
+ * of pufferl.py:359-361:
+ *     w = nan_to_num(seg_abs_sum ** alpha, 0, 0, 0)
+ *     p = (w + 1e-6) / (sum(w) + 1e-6)
+ * split in two launches so that a sharded caller can all-reduce the sum in
+ * between:
+ *   _weights : writes weights[s] and the fp64 total sum(w) into *total_w
+ *              (deterministic two-level reduction through `scratch`).
+ *   _probs   : writes probs[s] = (weights[s] + 1e-6) / (*total_w + 1e-6).
+ * scratch: device memory, at least puff_priorities_sm100_scratch_bytes(S)
+ * bytes, 8-byte aligned, owned by the caller; no allocation happens here.
+ */
+size_t puff_priorities_sm100_scratch_bytes(long long num_segments);
+int puff_priorities_sm100_weights(const float* seg_abs_sum, float* weights,
+                                  double* total_w, float alpha,
+                                  long long num_segments,
+                                  void* scratch, size_t scratch_bytes,
+                                  void* cuda_stream);
+int puff_priorities_sm100_probs(const float* weights, const double* total_w,
+                                float* probs, long long num_segments,
+                                void* cuda_stream);
+
+/* ---- introspection ------------------------------------------------------- */
+/* Human-readable text for a return code of any entry point above. */
+const char* puff_advantage_sm100_strerror(int code);
+/* PUFF_KERNEL_* used by the calling thread's most recent _launch. */
+int puff_advantage_sm100_last_kernel(void);
+/* Number of kernels this library has launched in this process so far. */
+long long puff_advantage_sm100_launch_count(void);
+/* Synchronises the current device and returns (then clears) the device-side
+ * status word: 0, or PUFF_ERR_DEVICE_WAIT when a bounded wait inside a kernel
+ * gave up.  Meant for tests and debugging; the launch path never calls it. */
+int puff_advantage_sm100_device_status(void);
+/* Library version, "major.minor". */
+const char* puff_advantage_sm100_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PUFF_ADVANTAGE_H_ */

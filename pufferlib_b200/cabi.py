@@ -1,0 +1,83 @@
+"""ctypes binding of the C ABI declared in include/puff_advantage.h.
+
+This is the stub a maintainer of the reference would add to reach the library
+without going through torch's dispatcher; the torch operator
+(`pufferlib_b200._C`) calls the same entry points from C++.  There is no CPU
+path behind any of these functions: when the shared library has not been built
+the import raises, and on a machine without an sm_100 GPU every launch returns
+an error code that `check()` turns into a RuntimeError.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libpuff_advantage_sm100.so")
+
+# error codes / variants / kernels of include/puff_advantage.h
+OK = 0
+ERR_NULL, ERR_SHAPE, ERR_VARIANT, ERR_ALIGN, ERR_ALIAS = -1, -2, -3, -4, -5
+ERR_ARCH, ERR_DRIVER, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_SIZE = -6, -7, -8, -9, -10
+VARIANT_AUTO, VARIANT_SERIAL, VARIANT_SCAN, VARIANT_GENERIC = 0, 1, 2, 3
+KERNEL_NONE, KERNEL_TMA2D, KERNEL_BULK1D, KERNEL_SCAN, KERNEL_GENERIC = 0, 1, 2, 3, 4
+VARIANTS = {"auto": VARIANT_AUTO, "serial": VARIANT_SERIAL, "scan": VARIANT_SCAN, "generic": VARIANT_GENERIC}
+KERNEL_NAMES = {KERNEL_NONE: "none", KERNEL_TMA2D: "tma2d", KERNEL_BULK1D: "bulk1d",
+                KERNEL_SCAN: "scan", KERNEL_GENERIC: "generic"}
+
+# every symbol the header declares, with its ctypes signature
+_P = ctypes.c_void_p
+_F = ctypes.c_float
+_LL = ctypes.c_longlong
+_I = ctypes.c_int
+SIGNATURES = {
+    "puff_advantage_sm100_launch": (_I, [_P] * 6 + [_F] * 4 + [_LL, _LL, _I, _P]),
+    "puff_advantage_sm100_host": (_I, [_P] * 6 + [_F] * 4 + [_LL, _LL, _I, _I]),
+    "puff_advantage_sm100_host_release": (_I, [_I]),
+    "puff_priorities_sm100_scratch_bytes": (ctypes.c_size_t, [_LL]),
+    "puff_priorities_sm100_weights": (_I, [_P, _P, _P, _F, _LL, _P, ctypes.c_size_t, _P]),
+    "puff_priorities_sm100_probs": (_I, [_P, _P, _P, _LL, _P]),
+    "puff_advantage_sm100_strerror": (ctypes.c_char_p, [_I]),
+    "puff_advantage_sm100_last_kernel": (_I, []),
+    "puff_advantage_sm100_launch_count": (_LL, []),
+    "puff_advantage_sm100_device_status": (_I, []),
+    "puff_advantage_sm100_version": (ctypes.c_char_p, []),
+}
+
+_lib = None
+
+
+def load():
+    """The loaded library (ctypes.CDLL) with argument types set."""
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} has not been built; run `python -m pufferlib_b200.build` "
+                "(needs nvcc with sm_100a support)")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def strerror(code):
+    return load().puff_advantage_sm100_strerror(int(code)).decode()
+
+
+def check(code, what="puff_advantage"):
+    if code != OK:
+        raise RuntimeError(f"{what}: {strerror(code)} (code {code})")
+
+
+def last_kernel():
+    return KERNEL_NAMES.get(load().puff_advantage_sm100_last_kernel(), "?")
+
+
+def launch_count():
+    return int(load().puff_advantage_sm100_launch_count())
+
+
+def device_status():
+    return int(load().puff_advantage_sm100_device_status())

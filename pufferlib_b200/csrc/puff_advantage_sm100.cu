@@ -1,0 +1,1033 @@
+// V-trace-clipped GAE advantage kernels for sm_100a and their C-ABI launcher.
+//
+// Torch-free on purpose: a standalone nvcc harness can #include this file, and
+// the torch operator binding only sees the extern "C" entry points declared in
+// include/puff_advantage.h.
+//
+// Replaces pufferlib/extensions/cuda/pufferlib.cu:7-82 of the reference (one
+// thread per segment walking global memory at a stride of `horizon` floats).
+// The op is a memory-bound linear recurrence: 20 algorithmic bytes and about
+// ten flops per element, so the design goal is HBM bandwidth, not flops.
+//
+// Kernels
+//   tma2d   serial, bit-exact.  One warp per CTA owns a tile of 32 segments;
+//           the horizon is walked backwards in chunks of 32 columns.  Each
+//           chunk of the four inputs arrives as a 32x32 TMA box in
+//           128B-swizzled shared memory behind an mbarrier ring, lane r runs
+//           row r's recurrence out of shared memory with conflict-free 128-bit
+//           reads, and the advantages leave through a TMA store whose tensor
+//           map is one column narrower than the row, so the hardware's bounds
+//           clipping keeps advantages[:, H-1] untouched.  Needs H % 4 == 0 and
+//           16-byte aligned base pointers.
+//   bulk1d  serial, bit-exact, for H % 4 != 0 (row pitch not a multiple of
+//           16 bytes, so no 2-D tensor map exists): tiles of 4..32 whole rows
+//           are contiguous spans, fetched with 1-D bulk copies.
+//   scan    T threads per row, 4 steps per thread: local affine composition,
+//           warp-shuffle + shared-memory scan of the (k, d) pairs, serial
+//           replay of the 4 steps from the scanned carry-in.  For long rows
+//           with few segments, where one thread per row cannot fill the GPU.
+//   generic serial, bit-exact, plain global loads.  Any alignment, any H.
+//
+// Every wait on an mbarrier is bounded: when the limit is hit the warp records
+// PUFF_ERR_DEVICE_WAIT in a status word, drains its own stores and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdlib.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "../../include/puff_advantage.h"
+
+namespace puff {
+
+// ---------------------------------------------------------------------------
+// device-side status word and launch counter
+// ---------------------------------------------------------------------------
+__device__ int g_device_status = 0;
+static std::atomic<long long> g_launch_count{0};
+static thread_local int t_last_kernel = PUFF_KERNEL_NONE;
+
+constexpr int kTileRows = 32;              // segments per warp tile
+constexpr int kChunkCols = 32;             // columns per TMA box (128 bytes)
+constexpr int kBoxBytes = kTileRows * kChunkCols * 4;   // 4096
+constexpr int kStageBytes = 4 * kBoxBytes;              // v, r, d, w
+constexpr uint32_t kWaitLimit = 1u << 24;  // mbarrier polls before giving up
+
+// ---------------------------------------------------------------------------
+// the recurrence step, in the reference's operation order
+// (pufferlib/extensions/pufferlib.cpp:34-38).  Explicit round-to-nearest
+// intrinsics are never contracted into FMAs, which is what keeps the serial
+// kernels bit-identical to the CPU build of the reference.  `1.0 - dones` is a
+// double subtraction there; for fp32 operands the fp32 subtraction rounds to
+// the same value (53 >= 2*24 + 2).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float adv_step(float v_t, float w_t, float v_n, float r_n,
+                                          float d_n, float a_next, float gamma, float gl,
+                                          float rho_clip, float c_clip)
+{
+    const float nn = __fsub_rn(1.0f, d_n);
+    const float rho = fminf(w_t, rho_clip);
+    const float c = fminf(w_t, c_clip);
+    const float td = __fsub_rn(__fadd_rn(r_n, __fmul_rn(__fmul_rn(gamma, v_n), nn)), v_t);
+    const float delta = __fmul_rn(rho, td);
+    const float carry = __fmul_rn(__fmul_rn(__fmul_rn(gl, c), a_next), nn);
+    return __fadd_rn(delta, carry);
+}
+
+// ---------------------------------------------------------------------------
+// PTX wrappers: mbarrier, TMA (non-multicast), bulk groups
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait; returns true when every lane of the warp saw the phase flip.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok = mbar_try_wait(bar, parity);
+    uint32_t polls = 0;
+    while (!ok && polls < kWaitLimit) {
+        ok = mbar_try_wait(bar, parity);
+        ++polls;
+    }
+    return __all_sync(0xffffffffu, ok != 0);
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int x, int y,
+                                            uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(tm), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, int x, int y, uint32_t src)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tm),
+                 "r"(x), "r"(y), "r"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
+                                             uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_commit()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
+}
+__device__ __forceinline__ float4 lds128(uint32_t addr)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, float4 v)
+{
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+                 "f"(v.w)
+                 : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// tma2d: serial, one warp per CTA, 32-row x 32-column TMA boxes
+// ---------------------------------------------------------------------------
+// Shared memory (offsets from a 1024-byte aligned base, which the 128B swizzle
+// pattern is anchored to):
+//   [0, NST*16K)            NST stages, each v | r | d | w boxes of 4 KB
+//   [NST*16K, NST*16K+8K)   two output boxes (ring for the TMA stores)
+//   then NST mbarriers
+// In a 128B-swizzled box the 16-byte unit q of row r sits at
+// r*128 + ((q ^ (r & 7)) << 4): lane r reading unit q of its own row touches
+// eight different units per quarter-warp, i.e. no bank conflicts.
+template <int NST>
+constexpr int tma2d_smem_bytes()
+{
+    return NST * kStageBytes + 2 * kBoxBytes + NST * 8 + 1024;
+}
+
+template <int NST, bool EPI>
+__global__ void __launch_bounds__(32)
+puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
+                      const __grid_constant__ CUtensorMap tm_r,
+                      const __grid_constant__ CUtensorMap tm_d,
+                      const __grid_constant__ CUtensorMap tm_w,
+                      const __grid_constant__ CUtensorMap tm_a,
+                      float* __restrict__ seg_abs_sum, float gamma, float lambda, float rho_clip,
+                      float c_clip, long long num_segments, int horizon, int num_tiles)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t out_base = base + NST * kStageBytes;
+    const uint32_t bar_base = out_base + 2 * kBoxBytes;
+    const int lane = threadIdx.x;
+
+    if (static_cast<int>(blockIdx.x) >= num_tiles) return;
+    const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                         static_cast<int>(gridDim.x);
+    const int nchunks = (horizon + kChunkCols - 1) / kChunkCols;
+    const int total = my_tiles * nchunks;
+
+    if (lane == 0) {
+        prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_r);
+        prefetch_tensormap(&tm_d);
+        prefetch_tensormap(&tm_w);
+        prefetch_tensormap(&tm_a);
+        for (int s = 0; s < NST; ++s) mbar_init(bar_base + 8 * s, 1);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncwarp();
+
+    // work item i -> (tile, chunk); chunks of a tile run from the last column block down
+    auto issue = [&](int i) {
+        const int k = i / nchunks;
+        const int c = nchunks - 1 - (i - k * nchunks);
+        const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+        const int s = i % NST;
+        const uint32_t st = base + s * kStageBytes;
+        const uint32_t bar = bar_base + 8 * s;
+        const int x = c * kChunkCols;
+        const int y = tile * kTileRows;
+        mbar_expect_tx(bar, kStageBytes);
+        tma_load_2d(st + 0 * kBoxBytes, &tm_v, x, y, bar);
+        tma_load_2d(st + 1 * kBoxBytes, &tm_r, x, y, bar);
+        tma_load_2d(st + 2 * kBoxBytes, &tm_d, x, y, bar);
+        tma_load_2d(st + 3 * kBoxBytes, &tm_w, x, y, bar);
+    };
+
+    if (lane == 0) {
+        const int pre = total < NST ? total : NST;
+        for (int i = 0; i < pre; ++i) issue(i);
+    }
+
+    const float gl = __fmul_rn(gamma, lambda);
+    const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
+    const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
+
+    float a_run = 0.0f, abs_run = 0.0f;
+    float nv = 0.0f, nr = 0.0f, nd = 0.0f;   // values/rewards/dones at column t+1 across units
+    int k = 0, c = nchunks - 1, s = 0;
+    uint32_t parity = 0;
+    bool failed = false;
+
+    for (int i = 0; i < total; ++i) {
+        // the output box i&1 was last read by the store of item i-2
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        if (!mbar_wait_warp(bar_base + 8 * s, parity)) {
+            failed = true;
+            break;
+        }
+        if (c == nchunks - 1) {
+            a_run = 0.0f;
+            abs_run = 0.0f;
+        }
+        const uint32_t st = base + s * kStageBytes;
+        const uint32_t ob = out_base + (i & 1) * kBoxBytes;
+        const int cbase = c * kChunkCols;
+#pragma unroll
+        for (int q = 7; q >= 0; --q) {
+            const int col0 = cbase + 4 * q;
+            if (col0 < horizon) {   // warp-uniform
+                const uint32_t off = row_off + ((static_cast<uint32_t>(q) ^ sw) << 4);
+                const float4 v4 = lds128(st + 0 * kBoxBytes + off);
+                const float4 r4 = lds128(st + 1 * kBoxBytes + off);
+                const float4 d4 = lds128(st + 2 * kBoxBytes + off);
+                const float4 w4 = lds128(st + 3 * kBoxBytes + off);
+                float4 a4;
+                // column col0+3 is H-1 in the last unit of a row: no step there
+                if (col0 + 4 < horizon) {
+                    a_run = adv_step(v4.w, w4.w, nv, nr, nd, a_run, gamma, gl, rho_clip, c_clip);
+                    if (EPI) abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                }
+                a4.w = a_run;
+                a_run = adv_step(v4.z, w4.z, v4.w, r4.w, d4.w, a_run, gamma, gl, rho_clip, c_clip);
+                if (EPI) abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                a4.z = a_run;
+                a_run = adv_step(v4.y, w4.y, v4.z, r4.z, d4.z, a_run, gamma, gl, rho_clip, c_clip);
+                if (EPI) abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                a4.y = a_run;
+                a_run = adv_step(v4.x, w4.x, v4.y, r4.y, d4.y, a_run, gamma, gl, rho_clip, c_clip);
+                if (EPI) abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                a4.x = a_run;
+                nv = v4.x;
+                nr = r4.x;
+                nd = d4.x;
+                sts128(ob + off, a4);
+            }
+        }
+        const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+        if (EPI && c == 0) {
+            const long long row = static_cast<long long>(tile) * kTileRows + lane;
+            if (row < num_segments) seg_abs_sum[row] = abs_run;
+        }
+        // generic-proxy reads of the stage and writes of the output box are
+        // ordered before the async-proxy operations issued below
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(&tm_a, cbase, tile * kTileRows, ob);
+            bulk_commit();
+            if (i + NST < total) issue(i + NST);
+        }
+        if (--c < 0) {
+            c = nchunks - 1;
+            ++k;
+        }
+        if (++s == NST) {
+            s = 0;
+            parity ^= 1u;
+        }
+    }
+    if (lane == 0) {
+        bulk_wait_all();
+        if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// bulk1d: serial, dense tiles of `tile_rows` whole rows fetched by 1-D bulk copies
+// ---------------------------------------------------------------------------
+// Shared memory: 2 stages x 4 arrays x tile_rows*H floats, then 2 mbarriers.
+// A tile is a contiguous span of tile_rows*H*4 bytes per array; tile_rows is a
+// multiple of 4, so every tile starts on a 16-byte boundary for any H.  The
+// last tile of the buffer may hold a row count whose byte size is not a
+// multiple of 16; it is fetched with plain loads instead.  Lane r < tile_rows
+// walks row r (stride H words: conflict-free for odd H), writes the advantages
+// over the consumed importance slot, and the warp then stores the tile with
+// coalesced stores that skip column H-1.
+__global__ void __launch_bounds__(32)
+puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
+                       const float* __restrict__ dones, const float* __restrict__ importance,
+                       float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
+                       float lambda, float rho_clip, float c_clip, long long num_segments,
+                       int horizon, int tile_rows, long long num_tiles)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+    float* const smem_f = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
+    const int lane = threadIdx.x;
+    const int tile_elems = tile_rows * horizon;
+    const uint32_t arr_bytes = static_cast<uint32_t>(tile_elems) * 4u;
+    const uint32_t arr_pitch = (arr_bytes + 15u) & ~15u;     // keep every array 16-byte aligned
+    const uint32_t stage_bytes = 4u * arr_pitch;
+    const uint32_t bar_base = base + 2u * stage_bytes;
+
+    if (static_cast<long long>(blockIdx.x) >= num_tiles) return;
+    const long long my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+    if (lane == 0) {
+        mbar_init(bar_base, 1);
+        mbar_init(bar_base + 8, 1);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncwarp();
+
+    const float* const src[4] = {values, rewards, dones, importance};
+
+    // rows in tile, and whether the tile can come in by bulk copy
+    auto tile_rows_of = [&](long long tile) {
+        const long long rem = num_segments - tile * tile_rows;
+        return static_cast<int>(rem < tile_rows ? rem : tile_rows);
+    };
+    auto fetch = [&](long long n, int s) {   // whole warp calls this
+        const long long tile = blockIdx.x + n * gridDim.x;
+        const int rows = tile_rows_of(tile);
+        const uint32_t bytes = static_cast<uint32_t>(rows) * horizon * 4u;
+        const long long goff = tile * tile_elems;
+        const uint32_t st = base + s * stage_bytes;
+        if ((bytes & 15u) == 0u) {
+            if (lane == 0) {
+                mbar_expect_tx(bar_base + 8 * s, 4u * bytes);
+                for (int a = 0; a < 4; ++a) bulk_load_1d(st + a * arr_pitch, src[a] + goff, bytes, bar_base + 8 * s);
+            }
+        } else {
+            float* const dst = smem_f + (s * stage_bytes) / 4;
+            const int n_el = rows * horizon;
+            for (int a = 0; a < 4; ++a) {
+                const float* g = src[a] + goff;
+                float* d = dst + (a * arr_pitch) / 4;
+                for (int e = lane; e < n_el; e += 32) d[e] = __ldg(g + e);
+            }
+        }
+    };
+    auto bulk_tile = [&](long long n) {
+        const long long tile = blockIdx.x + n * gridDim.x;
+        return ((static_cast<uint32_t>(tile_rows_of(tile)) * horizon * 4u) & 15u) == 0u;
+    };
+
+    fetch(0, 0);
+    const float gl = __fmul_rn(gamma, lambda);
+    uint32_t parity[2] = {0u, 0u};
+    bool failed = false;
+
+    for (long long n = 0; n < my_tiles; ++n) {
+        const int s = static_cast<int>(n & 1);
+        if (n + 1 < my_tiles) fetch(n + 1, s ^ 1);
+        if (bulk_tile(n)) {
+            if (!mbar_wait_warp(bar_base + 8 * s, parity[s])) {
+                failed = true;
+                break;
+            }
+            parity[s] ^= 1u;
+        } else {
+            __syncwarp();
+        }
+        const long long tile = blockIdx.x + n * gridDim.x;
+        const int rows = tile_rows_of(tile);
+        float* const sv = smem_f + (s * stage_bytes) / 4;
+        float* const sr = sv + arr_pitch / 4;
+        float* const sd = sr + arr_pitch / 4;
+        float* const swt = sd + arr_pitch / 4;
+        if (lane < rows) {
+            const int ro = lane * horizon;
+            float a_run = 0.0f, abs_run = 0.0f;
+            float v_n = sv[ro + horizon - 1];
+            for (int t = horizon - 2; t >= 0; --t) {
+                const float v_t = sv[ro + t];
+                a_run = adv_step(v_t, swt[ro + t], v_n, sr[ro + t + 1], sd[ro + t + 1], a_run, gamma,
+                                 gl, rho_clip, c_clip);
+                abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                swt[ro + t] = a_run;
+                v_n = v_t;
+            }
+            if (seg_abs_sum != nullptr) seg_abs_sum[tile * tile_rows + lane] = abs_run;
+        }
+        __syncwarp();
+        // coalesced copy-out, column H-1 of every row skipped
+        {
+            float* const g = advantages + tile * tile_elems;
+            const int n_el = rows * horizon;
+            const int n4 = n_el >> 2;   // tile start is 16-byte aligned
+            for (int e4 = lane; e4 < n4; e4 += 32) {
+                const int e = e4 << 2;
+                const float4 a4 = *reinterpret_cast<const float4*>(swt + e);
+                const int col = e % horizon;
+                if (col + 4 < horizon) {
+                    *reinterpret_cast<float4*>(g + e) = a4;
+                } else {
+                    const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int cj = (col + j) % horizon;
+                        if (cj != horizon - 1) g[e + j] = av[j];
+                    }
+                }
+            }
+            for (int e = (n4 << 2) + lane; e < n_el; e += 32)
+                if (e % horizon != horizon - 1) g[e] = swt[e];
+        }
+        // the stage is refilled by the async proxy two iterations from now
+        fence_proxy_async();
+        __syncwarp();
+    }
+    if (failed && lane == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+}
+
+// ---------------------------------------------------------------------------
+// scan: NT threads per row, 4 steps per thread, affine-pair scan of the carries
+// ---------------------------------------------------------------------------
+// A_t = delta_t + k_t * A_{t+1} with k_t = ((gamma*lambda)*c_t)*nn_t.  Thread j
+// of a pass owns the unit of four columns G-1-j counted from the end of the
+// row, so the suffix scan in time is an inclusive prefix scan over j.  The
+// composed pair (K, D) of a unit maps the advantage entering it (column 4g+4)
+// to the one leaving it (column 4g): A_out = D + K * A_in.  After the scan each
+// thread knows its own A_in and replays its four steps in the reference's
+// operation order, so only the carry-in differs from the serial result.
+template <bool VEC>
+__global__ void __launch_bounds__(1024)
+puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
+                     const float* __restrict__ dones, const float* __restrict__ importance,
+                     float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
+                     float lambda, float rho_clip, float c_clip, long long num_segments, int horizon)
+{
+    __shared__ float s_k[32], s_d[32], s_abs[32];
+    __shared__ float s_carry;
+    const int tid = threadIdx.x;
+    const int nt = blockDim.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int nwarps = nt >> 5;
+    const float gl = __fmul_rn(gamma, lambda);
+    const int units = (horizon + 3) >> 2;          // units of 4 columns per row
+    const int passes = (units + nt - 1) / nt;
+
+    for (long long row = blockIdx.x; row < num_segments; row += gridDim.x) {
+        const long long ro = row * horizon;
+        const float* const v = values + ro;
+        const float* const r = rewards + ro;
+        const float* const d = dones + ro;
+        const float* const w = importance + ro;
+        float* const a = advantages + ro;
+        float a_pass = 0.0f;      // advantage entering this pass (from later columns)
+        float abs_acc = 0.0f;     // thread 0 only
+
+        for (int p = 0; p < passes; ++p) {
+            const int j = p * nt + tid;
+            const int g = units - 1 - j;
+            const bool live = g >= 0;
+            const int col0 = g << 2;
+            float vv[5], rr[5], dd[5], ww[4];   // index i <-> column col0+i
+#pragma unroll
+            for (int i = 0; i < 5; ++i) {
+                vv[i] = 0.0f;
+                rr[i] = 0.0f;
+                dd[i] = 0.0f;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ww[i] = 0.0f;
+            if (live) {
+                if (VEC) {   // horizon % 4 == 0 and 16-byte aligned bases
+                    const float4 v4 = __ldg(reinterpret_cast<const float4*>(v + col0));
+                    const float4 r4 = __ldg(reinterpret_cast<const float4*>(r + col0));
+                    const float4 d4 = __ldg(reinterpret_cast<const float4*>(d + col0));
+                    const float4 w4 = __ldg(reinterpret_cast<const float4*>(w + col0));
+                    vv[0] = v4.x; vv[1] = v4.y; vv[2] = v4.z; vv[3] = v4.w;
+                    rr[0] = r4.x; rr[1] = r4.y; rr[2] = r4.z; rr[3] = r4.w;
+                    dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
+                    ww[0] = w4.x; ww[1] = w4.y; ww[2] = w4.z; ww[3] = w4.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (col0 + i < horizon) {
+                            vv[i] = __ldg(v + col0 + i);
+                            rr[i] = __ldg(r + col0 + i);
+                            dd[i] = __ldg(d + col0 + i);
+                            ww[i] = __ldg(w + col0 + i);
+                        }
+                    }
+                }
+                if (col0 + 4 < horizon) {
+                    vv[4] = __ldg(v + col0 + 4);
+                    rr[4] = __ldg(r + col0 + 4);
+                    dd[4] = __ldg(d + col0 + 4);
+                }
+            }
+            // local composition over the (up to) four steps, latest column first
+            float K = 1.0f, D = 0.0f;
+            float dl[4], kk[4];
+#pragma unroll
+            for (int i = 3; i >= 0; --i) {
+                const bool step = live && (col0 + i + 1 < horizon);   // t <= H-2
+                const float nn = __fsub_rn(1.0f, dd[i + 1]);
+                const float rho = fminf(ww[i], rho_clip);
+                const float c = fminf(ww[i], c_clip);
+                const float td = __fsub_rn(__fadd_rn(rr[i + 1], __fmul_rn(__fmul_rn(gamma, vv[i + 1]), nn)), vv[i]);
+                dl[i] = step ? __fmul_rn(rho, td) : 0.0f;
+                kk[i] = step ? __fmul_rn(__fmul_rn(gl, c), nn) : 1.0f;
+                D = fmaf(kk[i], D, dl[i]);
+                K = kk[i] * K;
+            }
+            // inclusive prefix scan over j inside the warp
+            float Ki = K, Di = D;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float Kp = __shfl_up_sync(0xffffffffu, Ki, o);
+                const float Dp = __shfl_up_sync(0xffffffffu, Di, o);
+                if (lane >= o) {
+                    Di = fmaf(Ki, Dp, Di);
+                    Ki = Ki * Kp;
+                }
+            }
+            // exclusive prefix inside the warp
+            float Ke = __shfl_up_sync(0xffffffffu, Ki, 1);
+            float De = __shfl_up_sync(0xffffffffu, Di, 1);
+            if (lane == 0) {
+                Ke = 1.0f;
+                De = 0.0f;
+            }
+            float a_in;
+            if (nwarps > 1) {
+                if (lane == 31) {
+                    s_k[warp] = Ki;
+                    s_d[warp] = Di;
+                }
+                __syncthreads();
+                if (warp == 0) {
+                    float Kw = lane < nwarps ? s_k[lane] : 1.0f;
+                    float Dw = lane < nwarps ? s_d[lane] : 0.0f;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const float Kp = __shfl_up_sync(0xffffffffu, Kw, o);
+                        const float Dp = __shfl_up_sync(0xffffffffu, Dw, o);
+                        if (lane >= o) {
+                            Dw = fmaf(Kw, Dp, Dw);
+                            Kw = Kw * Kp;
+                        }
+                    }
+                    // A leaving warp `lane` = Dw + Kw * a_pass: store it, the next warp enters with it
+                    s_d[lane] = fmaf(Kw, a_pass, Dw);
+                }
+                __syncthreads();
+                const float a_warp_in = warp == 0 ? a_pass : s_d[warp - 1];
+                a_in = fmaf(Ke, a_warp_in, De);
+                if (tid == 0) s_carry = s_d[nwarps - 1];
+            } else {
+                a_in = fmaf(Ke, a_pass, De);
+                const float a_out = fmaf(Ki, a_pass, Di);
+                if (tid == 31) s_carry = a_out;
+            }
+            // replay in the reference's operation order
+            float a_run = a_in, abs_loc = 0.0f;
+            float out[4];
+#pragma unroll
+            for (int i = 3; i >= 0; --i) {
+                const bool step = live && (col0 + i + 1 < horizon);
+                if (step) {
+                    a_run = adv_step(vv[i], ww[i], vv[i + 1], rr[i + 1], dd[i + 1], a_run, gamma, gl,
+                                     rho_clip, c_clip);
+                    abs_loc += fabsf(a_run);
+                }
+                out[i] = a_run;
+            }
+            if (live) {
+                if (VEC && col0 + 4 < horizon) {
+                    *reinterpret_cast<float4*>(a + col0) = make_float4(out[0], out[1], out[2], out[3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (col0 + i + 1 < horizon) a[col0 + i] = out[i];
+                }
+            }
+            if (seg_abs_sum != nullptr) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) abs_loc += __shfl_xor_sync(0xffffffffu, abs_loc, o);
+                if (lane == 0) s_abs[warp] = abs_loc;
+            }
+            __syncthreads();   // s_carry, s_abs visible; s_k / s_d reusable
+            a_pass = s_carry;
+            if (seg_abs_sum != nullptr && tid == 0)
+                for (int i = 0; i < nwarps; ++i) abs_acc += s_abs[i];
+            __syncthreads();
+        }
+        if (seg_abs_sum != nullptr && tid == 0) seg_abs_sum[row] = abs_acc;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// generic: serial, one thread per row, plain global loads
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+puff_adv_generic_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
+                        const float* __restrict__ dones, const float* __restrict__ importance,
+                        float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
+                        float lambda, float rho_clip, float c_clip, long long num_segments,
+                        long long horizon)
+{
+    const float gl = __fmul_rn(gamma, lambda);
+    for (long long row = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+         row < num_segments; row += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long ro = row * horizon;
+        float a_run = 0.0f, abs_run = 0.0f;
+        float v_n = __ldg(values + ro + horizon - 1);
+        for (long long t = horizon - 2; t >= 0; --t) {
+            const float v_t = __ldg(values + ro + t);
+            a_run = adv_step(v_t, __ldg(importance + ro + t), v_n, __ldg(rewards + ro + t + 1),
+                             __ldg(dones + ro + t + 1), a_run, gamma, gl, rho_clip, c_clip);
+            abs_run = __fadd_rn(abs_run, fabsf(a_run));
+            advantages[ro + t] = a_run;
+            v_n = v_t;
+        }
+        if (seg_abs_sum != nullptr) seg_abs_sum[row] = abs_run;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+struct DeviceInfo {
+    int sm_count = 0;
+    int cc_major = 0;
+    int max_smem_optin = 0;
+    cudaError_t err = cudaSuccess;
+    bool ready = false;
+};
+static DeviceInfo g_dev[64];
+static std::mutex g_dev_mutex;
+
+static const DeviceInfo* device_info(int* code)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        *code = static_cast<int>(e);
+        return nullptr;
+    }
+    if (dev < 0 || dev >= 64) {
+        *code = PUFF_ERR_ARCH;
+        return nullptr;
+    }
+    DeviceInfo& d = g_dev[dev];
+    if (!d.ready) {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        if (!d.ready) {
+            cudaError_t e1 = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+            cudaError_t e2 = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+            cudaError_t e3 = cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+            d.err = e1 != cudaSuccess ? e1 : (e2 != cudaSuccess ? e2 : e3);
+            if (d.err == cudaSuccess) {
+                // opt in to large dynamic shared memory once per device
+                cudaFuncSetAttribute(puff_adv_tma2d_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<2>());
+                cudaFuncSetAttribute(puff_adv_tma2d_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<2>());
+                cudaFuncSetAttribute(puff_adv_tma2d_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<3>());
+                cudaFuncSetAttribute(puff_adv_tma2d_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<3>());
+                cudaFuncSetAttribute(puff_adv_tma2d_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<4>());
+                cudaFuncSetAttribute(puff_adv_tma2d_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<4>());
+                cudaFuncSetAttribute(puff_adv_bulk1d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem_optin);
+                d.err = cudaGetLastError();
+            }
+            d.ready = (d.err == cudaSuccess);
+        }
+    }
+    if (d.err != cudaSuccess) {
+        *code = static_cast<int>(d.err);
+        return nullptr;
+    }
+    if (d.cc_major != 10) {
+        *code = PUFF_ERR_ARCH;
+        return nullptr;
+    }
+    return &d;
+}
+
+// cuTensorMapEncodeTiled through the runtime, so the library has no link-time
+// dependency on libcuda
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// [rows, width] fp32 view with a row pitch of `pitch_elems` floats, 32x32 boxes, 128B swizzle
+static bool make_map(CUtensorMap* tm, const float* base, long long rows, long long width, long long pitch_elems)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 4u};
+    const cuuint32_t box[2] = {kChunkCols, kTileRows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct MapSet {
+    const float* ptr[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    long long rows = -1, horizon = -1;
+    CUtensorMap tm[5];
+};
+
+static int env_int(const char* name, int fallback)
+{
+    const char* s = getenv(name);
+    if (s == nullptr || *s == '\0') return fallback;
+    return atoi(s);
+}
+
+template <int NST>
+static cudaError_t launch_tma2d(const MapSet& m, float* seg_abs_sum, float gamma, float lambda, float rho_clip,
+                                float c_clip, long long rows, int horizon, int grid, int tiles, cudaStream_t st)
+{
+    if (seg_abs_sum != nullptr)
+        puff_adv_tma2d_kernel<NST, true><<<grid, 32, tma2d_smem_bytes<NST>(), st>>>(
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], seg_abs_sum, gamma, lambda, rho_clip, c_clip, rows,
+            horizon, tiles);
+    else
+        puff_adv_tma2d_kernel<NST, false><<<grid, 32, tma2d_smem_bytes<NST>(), st>>>(
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], nullptr, gamma, lambda, rho_clip, c_clip, rows,
+            horizon, tiles);
+    return cudaGetLastError();
+}
+
+static bool ranges_overlap(const void* a, size_t na, const void* b, size_t nb)
+{
+    const uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
+    return a0 < b0 + nb && b0 < a0 + na;
+}
+
+// bulk1d tile height: the largest of 32/16/8/4 rows whose two stages stay
+// within ~40 KB (so that several CTAs share an SM), else whatever still fits
+static int bulk1d_tile_rows(long long horizon, int max_smem, size_t* smem_bytes)
+{
+    const int cand[4] = {32, 16, 8, 4};
+    int best = 0;
+    size_t best_bytes = 0;
+    for (int i = 0; i < 4; ++i) {
+        const size_t arr = (static_cast<size_t>(cand[i]) * horizon * 4 + 15) & ~static_cast<size_t>(15);
+        const size_t need = 2 * 4 * arr + 16 + 128;
+        if (need > static_cast<size_t>(max_smem)) continue;
+        if (best == 0) {
+            best = cand[i];
+            best_bytes = need;
+        }
+        if (need <= 40 * 1024) {
+            best = cand[i];
+            best_bytes = need;
+            break;
+        }
+        best = cand[i];
+        best_bytes = need;
+    }
+    *smem_bytes = best_bytes;
+    return best;
+}
+
+}  // namespace puff
+
+using namespace puff;
+
+extern "C" int puff_advantage_sm100_launch(const float* values, const float* rewards, const float* dones,
+                                           const float* importance, float* advantages, float* seg_abs_sum,
+                                           float gamma, float lambda, float rho_clip, float c_clip,
+                                           long long num_segments, long long horizon, int variant,
+                                           void* cuda_stream)
+{
+    t_last_kernel = PUFF_KERNEL_NONE;
+    if (num_segments < 0 || horizon < 0) return PUFF_ERR_SHAPE;
+    if (variant < PUFF_VARIANT_AUTO || variant > PUFF_VARIANT_GENERIC) return PUFF_ERR_VARIANT;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    if (num_segments == 0) return PUFF_OK;
+    if (horizon < 2) {
+        // no step exists: nothing is written to advantages, the sums are empty
+        if (seg_abs_sum != nullptr) {
+            cudaError_t e = cudaMemsetAsync(seg_abs_sum, 0, static_cast<size_t>(num_segments) * 4, st);
+            if (e != cudaSuccess) return static_cast<int>(e);
+        }
+        return PUFF_OK;
+    }
+    if (values == nullptr || rewards == nullptr || dones == nullptr || importance == nullptr ||
+        advantages == nullptr)
+        return PUFF_ERR_NULL;
+    const void* ptrs[6] = {values, rewards, dones, importance, advantages, seg_abs_sum};
+    bool aligned16 = true;
+    for (int i = 0; i < 6; ++i) {
+        const uintptr_t p = reinterpret_cast<uintptr_t>(ptrs[i]);
+        if (p & 3u) return PUFF_ERR_ALIGN;
+        if (i < 5 && (p & 15u)) aligned16 = false;
+    }
+    const size_t bytes = static_cast<size_t>(num_segments) * static_cast<size_t>(horizon) * 4;
+    for (int i = 0; i < 4; ++i) {
+        if (ranges_overlap(advantages, bytes, ptrs[i], bytes)) return PUFF_ERR_ALIAS;
+        if (seg_abs_sum != nullptr && ranges_overlap(seg_abs_sum, static_cast<size_t>(num_segments) * 4, ptrs[i], bytes))
+            return PUFF_ERR_ALIAS;
+    }
+    if (seg_abs_sum != nullptr && ranges_overlap(seg_abs_sum, static_cast<size_t>(num_segments) * 4, advantages, bytes))
+        return PUFF_ERR_ALIAS;
+
+    int code = 0;
+    const DeviceInfo* dev = device_info(&code);
+    if (dev == nullptr) return code;
+
+    // ---- choose the kernel -------------------------------------------------
+    size_t bulk_smem = 0;
+    const int bulk_rows = (aligned16 && horizon < (1 << 20)) ? bulk1d_tile_rows(horizon, dev->max_smem_optin, &bulk_smem) : 0;
+    const bool can_tma2d = aligned16 && (horizon % 4 == 0) && horizon <= 0x7fffffffLL - 64;
+    const bool can_bulk1d = bulk_rows > 0;
+    const bool can_scan = horizon <= 0x7fffffffLL - 8;
+    int kernel;
+    if (variant == PUFF_VARIANT_GENERIC) {
+        kernel = PUFF_KERNEL_GENERIC;
+    } else if (variant == PUFF_VARIANT_SCAN) {
+        kernel = can_scan ? PUFF_KERNEL_SCAN : PUFF_KERNEL_GENERIC;
+    } else {
+        const int serial_kernel = can_tma2d ? PUFF_KERNEL_TMA2D : (can_bulk1d ? PUFF_KERNEL_BULK1D : PUFF_KERNEL_GENERIC);
+        // long rows with too few segments to give every SM a few rows: scan
+        const bool few_rows = num_segments < static_cast<long long>(dev->sm_count) * 24;
+        if (variant == PUFF_VARIANT_AUTO && can_scan && few_rows && horizon >= 512)
+            kernel = PUFF_KERNEL_SCAN;
+        else
+            kernel = serial_kernel;
+    }
+    {
+        const int forced = env_int("PUFF_ADV_FORCE_KERNEL", 0);   // tests: 1..4
+        if (forced == PUFF_KERNEL_TMA2D && can_tma2d) kernel = forced;
+        if (forced == PUFF_KERNEL_BULK1D && can_bulk1d) kernel = forced;
+        if (forced == PUFF_KERNEL_SCAN && can_scan) kernel = forced;
+        if (forced == PUFF_KERNEL_GENERIC) kernel = forced;
+    }
+
+    cudaError_t err = cudaSuccess;
+    if (kernel == PUFF_KERNEL_TMA2D) {
+        // TMA coordinates are 32-bit: process blocks of at most 2^30 rows
+        const long long block_rows = 1LL << 30;
+        static thread_local MapSet cache;
+        const int nst = env_int("PUFF_ADV_STAGES", 3);
+        const int ctas_per_sm = nst <= 2 ? 5 : 3;
+        for (long long r0 = 0; r0 < num_segments && err == cudaSuccess; r0 += block_rows) {
+            const long long rows = num_segments - r0 < block_rows ? num_segments - r0 : block_rows;
+            const long long off = r0 * horizon;
+            const float* p[5] = {values + off, rewards + off, dones + off, importance + off, advantages + off};
+            bool hit = cache.rows == rows && cache.horizon == horizon;
+            for (int i = 0; i < 5 && hit; ++i) hit = cache.ptr[i] == p[i];
+            if (!hit) {
+                cache.rows = -1;
+                for (int i = 0; i < 4; ++i)
+                    if (!make_map(&cache.tm[i], p[i], rows, horizon, horizon)) return PUFF_ERR_DRIVER;
+                // one column narrower: stores to column H-1 are clipped by the hardware
+                if (!make_map(&cache.tm[4], p[4], rows, horizon - 1, horizon)) return PUFF_ERR_DRIVER;
+                for (int i = 0; i < 5; ++i) cache.ptr[i] = p[i];
+                cache.rows = rows;
+                cache.horizon = horizon;
+            }
+            const long long tiles = (rows + kTileRows - 1) / kTileRows;
+            const long long max_grid = static_cast<long long>(dev->sm_count) * ctas_per_sm;
+            const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
+            float* abs_p = seg_abs_sum != nullptr ? seg_abs_sum + r0 : nullptr;
+            if (nst <= 2)
+                err = launch_tma2d<2>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st);
+            else if (nst == 3)
+                err = launch_tma2d<3>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st);
+            else
+                err = launch_tma2d<4>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st);
+            g_launch_count.fetch_add(1, std::memory_order_relaxed);
+        }
+    } else if (kernel == PUFF_KERNEL_BULK1D) {
+        const long long tiles = (num_segments + bulk_rows - 1) / bulk_rows;
+        const int per_sm = static_cast<int>(static_cast<size_t>(dev->max_smem_optin) / (bulk_smem + 1024));
+        const long long max_grid = static_cast<long long>(dev->sm_count) * (per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm));
+        const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
+        puff_adv_bulk1d_kernel<<<grid, 32, bulk_smem, st>>>(values, rewards, dones, importance, advantages,
+                                                            seg_abs_sum, gamma, lambda, rho_clip, c_clip,
+                                                            num_segments, static_cast<int>(horizon), bulk_rows, tiles);
+        err = cudaGetLastError();
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    } else if (kernel == PUFF_KERNEL_SCAN) {
+        const long long units = (horizon + 3) / 4;
+        int nt = 32;
+        while (nt < 1024 && nt < units) nt <<= 1;
+        const long long max_grid = static_cast<long long>(dev->sm_count) * (2048 / nt) ;
+        const int grid = static_cast<int>(num_segments < max_grid ? num_segments : max_grid);
+        if (aligned16 && horizon % 4 == 0)
+            puff_adv_scan_kernel<true><<<grid, nt, 0, st>>>(values, rewards, dones, importance, advantages, seg_abs_sum,
+                                                            gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon));
+        else
+            puff_adv_scan_kernel<false><<<grid, nt, 0, st>>>(values, rewards, dones, importance, advantages, seg_abs_sum,
+                                                             gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon));
+        err = cudaGetLastError();
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    } else {
+        const long long blocks = (num_segments + 127) / 128;
+        const long long max_grid = static_cast<long long>(dev->sm_count) * 16;
+        const int grid = static_cast<int>(blocks < max_grid ? blocks : max_grid);
+        puff_adv_generic_kernel<<<grid, 128, 0, st>>>(values, rewards, dones, importance, advantages, seg_abs_sum,
+                                                      gamma, lambda, rho_clip, c_clip, num_segments, horizon);
+        err = cudaGetLastError();
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    }
+    t_last_kernel = kernel;
+    return static_cast<int>(err);
+}
+
+extern "C" const char* puff_advantage_sm100_strerror(int code)
+{
+    switch (code) {
+        case PUFF_OK: return "success";
+        case PUFF_ERR_NULL: return "a required pointer is NULL";
+        case PUFF_ERR_SHAPE: return "num_segments and horizon must be non-negative";
+        case PUFF_ERR_VARIANT: return "unknown kernel variant";
+        case PUFF_ERR_ALIGN: return "pointers must be 4-byte aligned";
+        case PUFF_ERR_ALIAS: return "output buffers must not overlap the inputs";
+        case PUFF_ERR_ARCH: return "the current CUDA device is not compute capability 10.x (sm_100a build)";
+        case PUFF_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor map";
+        case PUFF_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel gave up";
+        case PUFF_ERR_WORKSPACE: return "scratch or workspace missing, misaligned or too small";
+        case PUFF_ERR_SIZE: return "size beyond what this entry point supports";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    return "unknown error code";
+}
+
+extern "C" int puff_advantage_sm100_last_kernel(void) { return t_last_kernel; }
+
+extern "C" long long puff_advantage_sm100_launch_count(void)
+{
+    return g_launch_count.load(std::memory_order_relaxed);
+}
+
+namespace puff {
+void count_launch() { g_launch_count.fetch_add(1, std::memory_order_relaxed); }
+}
+
+extern "C" int puff_advantage_sm100_device_status(void)
+{
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    int h = 0;
+    e = cudaMemcpyFromSymbol(&h, g_device_status, sizeof(int));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (h != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+    }
+    return h;
+}
+
+extern "C" const char* puff_advantage_sm100_version(void) { return "0.1"; }

@@ -1,0 +1,180 @@
+// PyTorch operator boundary of the sm_100a advantage library.
+//
+// Takes the place of both translation units of the reference extension
+// `pufferlib._C`: pufferlib/extensions/pufferlib.cpp (module init :7-24, schema
+// :87-89) and pufferlib/extensions/cuda/pufferlib.cu (argument checks :22-38,
+// launcher :53-82, CUDA registration :84-86).  The operator namespace, name
+// and schema string are the reference's, so
+//   torch.ops.pufferlib.compute_puff_advantage(values, rewards, dones,
+//       importance, advantages, gamma, lambda, rho_clip, c_clip)
+// resolves here with pufferl.py:674 unchanged.  Only a CUDA kernel is
+// registered: CPU tensors raise the dispatcher's "no kernel for backend" error
+// instead of silently computing somewhere else.
+//
+// This file holds no arithmetic; it validates tensors, picks up the current
+// device and stream, and calls the C ABI of include/puff_advantage.h.
+#include <Python.h>
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/all.h>
+#include <torch/library.h>
+
+#include <cstdlib>
+#include <tuple>
+
+#include "../../include/puff_advantage.h"
+
+extern "C" {
+// Empty importable module: importing it loads this shared object, which runs
+// the TORCH_LIBRARY registrations below (same device as pufferlib.cpp:7-24).
+PyObject* PyInit__C(void)
+{
+    static struct PyModuleDef module_def = {PyModuleDef_HEAD_INIT, "_C", nullptr, -1, nullptr};
+    return PyModule_Create(&module_def);
+}
+}
+
+namespace pufferlib_b200 {
+
+static void check_rc(int rc, const char* what)
+{
+    TORCH_CHECK(rc == PUFF_OK, what, ": ", puff_advantage_sm100_strerror(rc), " (code ", rc, ")");
+}
+
+// Same rules and messages as vtrace_check_cuda (cu:22-38), except that a
+// non-contiguous tensor is an error: the reference calls t.contiguous() and
+// drops the result (cu:34-36), then reads the strided storage as if dense.
+static void check_inputs(std::initializer_list<torch::Tensor> tensors, const torch::Tensor& values)
+{
+    const auto device = values.device();
+    const int64_t num_steps = values.dim() > 0 ? values.size(0) : 0;
+    const int64_t horizon = values.dim() > 1 ? values.size(1) : 0;
+    for (const torch::Tensor& t : tensors) {
+        TORCH_CHECK(t.dim() == 2, "Tensor must be 2D");
+        TORCH_CHECK(t.device() == device, "All tensors must be on same device");
+        TORCH_CHECK(t.size(0) == num_steps, "First dimension must match num_steps");
+        TORCH_CHECK(t.size(1) == horizon, "Second dimension must match horizon");
+        TORCH_CHECK(t.dtype() == torch::kFloat32, "All tensors must be float32");
+        TORCH_CHECK(t.is_contiguous(), "All tensors must be contiguous");
+    }
+    TORCH_CHECK(values.is_cuda(), "All tensors must be on GPU");
+}
+
+static int variant_from_env()
+{
+    const char* s = std::getenv("PUFFER_ADV_VARIANT");
+    if (s == nullptr) return PUFF_VARIANT_AUTO;
+    const std::string v(s);
+    if (v == "serial") return PUFF_VARIANT_SERIAL;
+    if (v == "scan") return PUFF_VARIANT_SCAN;
+    if (v == "generic") return PUFF_VARIANT_GENERIC;
+    return PUFF_VARIANT_AUTO;
+}
+
+// compute_puff_advantage_cuda of cu:53-82
+void compute_puff_advantage_cuda(torch::Tensor values, torch::Tensor rewards, torch::Tensor dones,
+                                 torch::Tensor importance, torch::Tensor advantages, double gamma,
+                                 double lambda, double rho_clip, double c_clip)
+{
+    check_inputs({values, rewards, dones, importance, advantages}, values);
+    const c10::cuda::CUDAGuard guard(values.device());
+    const int rc = puff_advantage_sm100_launch(
+        values.data_ptr<float>(), rewards.data_ptr<float>(), dones.data_ptr<float>(),
+        importance.data_ptr<float>(), advantages.data_ptr<float>(), nullptr,
+        static_cast<float>(gamma), static_cast<float>(lambda), static_cast<float>(rho_clip),
+        static_cast<float>(c_clip), values.size(0), values.size(1), variant_from_env(),
+        at::cuda::getCurrentCUDAStream().stream());
+    check_rc(rc, "compute_puff_advantage");
+}
+
+// Sibling op: the same launch with the fused epilogue.  seg_abs_sum[s] receives
+// sum_t |advantages[s, t]| over t < H-1, what pufferl.py:359 computes with a
+// second pass over a zero-initialised `advantages`.
+void compute_puff_advantage_prio_cuda(torch::Tensor values, torch::Tensor rewards, torch::Tensor dones,
+                                      torch::Tensor importance, torch::Tensor advantages,
+                                      torch::Tensor seg_abs_sum, double gamma, double lambda,
+                                      double rho_clip, double c_clip)
+{
+    check_inputs({values, rewards, dones, importance, advantages}, values);
+    TORCH_CHECK(seg_abs_sum.dim() == 1 && seg_abs_sum.size(0) == values.size(0),
+                "seg_abs_sum must be 1D with one entry per segment");
+    TORCH_CHECK(seg_abs_sum.device() == values.device(), "All tensors must be on same device");
+    TORCH_CHECK(seg_abs_sum.dtype() == torch::kFloat32, "All tensors must be float32");
+    TORCH_CHECK(seg_abs_sum.is_contiguous(), "All tensors must be contiguous");
+    const c10::cuda::CUDAGuard guard(values.device());
+    const int rc = puff_advantage_sm100_launch(
+        values.data_ptr<float>(), rewards.data_ptr<float>(), dones.data_ptr<float>(),
+        importance.data_ptr<float>(), advantages.data_ptr<float>(), seg_abs_sum.data_ptr<float>(),
+        static_cast<float>(gamma), static_cast<float>(lambda), static_cast<float>(rho_clip),
+        static_cast<float>(c_clip), values.size(0), values.size(1), variant_from_env(),
+        at::cuda::getCurrentCUDAStream().stream());
+    check_rc(rc, "compute_puff_advantage_prio");
+}
+
+// pufferl.py:360 plus the sum of :361: weights and their fp64 total.
+std::tuple<torch::Tensor, torch::Tensor> puff_priority_weights_cuda(torch::Tensor seg_abs_sum, double alpha)
+{
+    TORCH_CHECK(seg_abs_sum.is_cuda(), "All tensors must be on GPU");
+    TORCH_CHECK(seg_abs_sum.dim() == 1 && seg_abs_sum.dtype() == torch::kFloat32 && seg_abs_sum.is_contiguous(),
+                "seg_abs_sum must be a contiguous 1D float32 tensor");
+    const c10::cuda::CUDAGuard guard(seg_abs_sum.device());
+    const int64_t n = seg_abs_sum.size(0);
+    auto weights = torch::empty_like(seg_abs_sum);
+    auto total = torch::empty({1}, seg_abs_sum.options().dtype(torch::kFloat64));
+    const size_t sbytes = puff_priorities_sm100_scratch_bytes(n);
+    auto scratch = torch::empty({static_cast<int64_t>((sbytes + 7) / 8)}, seg_abs_sum.options().dtype(torch::kFloat64));
+    const int rc = puff_priorities_sm100_weights(seg_abs_sum.data_ptr<float>(), weights.data_ptr<float>(),
+                                                 total.data_ptr<double>(), static_cast<float>(alpha), n,
+                                                 scratch.data_ptr<double>(), sbytes,
+                                                 at::cuda::getCurrentCUDAStream().stream());
+    check_rc(rc, "puff_priority_weights");
+    return {weights, total};
+}
+
+// pufferl.py:361 given the (possibly all-reduced) total.
+torch::Tensor puff_priority_probs_cuda(torch::Tensor weights, torch::Tensor total_w)
+{
+    TORCH_CHECK(weights.is_cuda() && total_w.is_cuda(), "All tensors must be on GPU");
+    TORCH_CHECK(weights.dim() == 1 && weights.dtype() == torch::kFloat32 && weights.is_contiguous(),
+                "weights must be a contiguous 1D float32 tensor");
+    TORCH_CHECK(total_w.numel() == 1 && total_w.dtype() == torch::kFloat64, "total_w must hold one float64");
+    const c10::cuda::CUDAGuard guard(weights.device());
+    auto probs = torch::empty_like(weights);
+    const int rc = puff_priorities_sm100_probs(weights.data_ptr<float>(), total_w.data_ptr<double>(),
+                                               probs.data_ptr<float>(), weights.size(0),
+                                               at::cuda::getCurrentCUDAStream().stream());
+    check_rc(rc, "puff_priority_probs");
+    return probs;
+}
+
+// Shape-only kernels so the ops can be traced (torch.compile / fake tensors).
+void compute_puff_advantage_meta(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor,
+                                 double, double, double, double) {}
+void compute_puff_advantage_prio_meta(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor,
+                                      torch::Tensor, double, double, double, double) {}
+
+TORCH_LIBRARY(pufferlib, m)
+{
+    // byte-identical to pufferlib.cpp:88
+    m.def("compute_puff_advantage(Tensor(a!) values, Tensor(b!) rewards, Tensor(c!) dones, Tensor(d!) importance, Tensor(e!) advantages, float gamma, float lambda, float rho_clip, float c_clip) -> ()");
+    m.def("compute_puff_advantage_prio(Tensor values, Tensor rewards, Tensor dones, Tensor importance, Tensor(a!) advantages, Tensor(b!) seg_abs_sum, float gamma, float lambda, float rho_clip, float c_clip) -> ()");
+    m.def("puff_priority_weights(Tensor seg_abs_sum, float alpha) -> (Tensor, Tensor)");
+    m.def("puff_priority_probs(Tensor weights, Tensor total_w) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(pufferlib, CUDA, m)
+{
+    m.impl("compute_puff_advantage", &compute_puff_advantage_cuda);
+    m.impl("compute_puff_advantage_prio", &compute_puff_advantage_prio_cuda);
+    m.impl("puff_priority_weights", &puff_priority_weights_cuda);
+    m.impl("puff_priority_probs", &puff_priority_probs_cuda);
+}
+
+TORCH_LIBRARY_IMPL(pufferlib, Meta, m)
+{
+    m.impl("compute_puff_advantage", &compute_puff_advantage_meta);
+    m.impl("compute_puff_advantage_prio", &compute_puff_advantage_prio_meta);
+}
+
+}  // namespace pufferlib_b200

@@ -1,0 +1,97 @@
+"""CPU: the oracle against the golden fixtures and the reference build."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import SENTINEL, bits_equal, first_mismatch, oracle_advantage, sha256_arrays
+from pufferlib_b200.workloads import WORKLOADS, Workload, make_inputs, shard_rows
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_oracle_matches_golden_small(golden_small):
+    """Fixtures were produced by the reference's own CPU op (make_golden.py)."""
+    for name, case in golden_small.items():
+        got = oracle_advantage([case[k] for k in ("values", "rewards", "dones", "importance")], case["hyper"])
+        assert bits_equal(got, case["advantages"]), f"{name}: {first_mismatch(got, case['advantages'])}"
+
+
+def test_last_column_untouched(golden_small):
+    for name, case in golden_small.items():
+        assert np.all(case["advantages"][:, -1] == np.float32(SENTINEL)), name
+
+
+@pytest.mark.parametrize("name", ["cfg0", "cfg1", "cfg3", "cfg4"])
+def test_oracle_matches_config_digest(name, config_digests):
+    wl = WORKLOADS[name]
+    inputs = make_inputs(wl)
+    ref = config_digests["configs"][name]
+    if sha256_arrays(*[t.numpy() for t in inputs]) != ref["inputs_sha256"]:
+        pytest.skip("this torch build draws different random inputs than the fixture generator")
+    got = oracle_advantage([t.numpy() for t in inputs], wl.hyper(), ref_sentinel(config_digests))
+    assert sha256_arrays(got) == ref["advantages_sha256"]
+    flat = got.reshape(-1)
+    assert flat[np.array(ref["sample_index"])].view(np.uint32).tolist() == ref["sample_bits"]
+
+
+def ref_sentinel(digests):
+    return digests["sentinel"]
+
+
+def test_oracle_matches_reference_build():
+    """Live bit-equality with the reference source compiled into oracle/_ref/
+    (present where the reference tree was mounted at build time)."""
+    from oracle import puff_oracle
+    ref = puff_oracle.load_reference()
+    if ref is None:
+        pytest.skip("oracle/_ref/ not built on this machine")
+    for wl in [WORKLOADS["cfg0"], WORKLOADS["cfg4"], Workload("x", 300, 91, seed=3, c_clip=0.0),
+               WORKLOADS["cfg3"]]:
+        inputs = make_inputs(wl)
+        adv = torch.full_like(inputs[0], SENTINEL)
+        ref(*inputs, adv, *wl.hyper())
+        got = oracle_advantage([t.numpy() for t in inputs], wl.hyper())
+        assert bits_equal(got, adv.numpy()), first_mismatch(got, adv.numpy())
+
+
+def test_plain_gae_cross_check():
+    """With importance == 1 and clips >= 1 the op is ordinary GAE whose last
+    step bootstraps nothing (compare pufferlib/cleanrl_ppo_atari.py:243-256,
+    which differs only in bootstrapping from next_value at the last step)."""
+    wl = Workload("gae", 6, 20, seed=21, done_p=0.15)
+    v, r, d, _ = [t.double().numpy() for t in make_inputs(wl)]
+    w = np.ones_like(v, dtype=np.float32)
+    got = oracle_advantage([v, r, d, w], wl.hyper(), sentinel=0.0)
+    exp = np.zeros_like(v)
+    last = np.zeros(v.shape[0])
+    for t in range(v.shape[1] - 2, -1, -1):
+        nn = 1.0 - d[:, t + 1]
+        delta = r[:, t + 1] + wl.gamma * v[:, t + 1] * nn - v[:, t]
+        last = delta + wl.gamma * wl.lam * nn * last
+        exp[:, t] = last
+    np.testing.assert_allclose(got, exp, rtol=2e-5, atol=2e-6)
+
+
+def test_abs_sum_and_priorities():
+    from oracle import puff_oracle
+    wl = WORKLOADS["cfg0"]
+    inputs = [t.numpy() for t in make_inputs(wl)]
+    adv = oracle_advantage(inputs, wl.hyper(), sentinel=0.0)
+    s = puff_oracle.abs_sum(adv)
+    np.testing.assert_allclose(s, np.abs(adv.astype(np.float64)).sum(1), rtol=1e-12)
+    w, p, tot = puff_oracle.priorities(s, 0.8)
+    t = torch.from_numpy(s)
+    tw = torch.nan_to_num(t ** 0.8, 0, 0, 0)
+    np.testing.assert_allclose(w, tw.numpy(), rtol=1e-12)
+    np.testing.assert_allclose(p, ((tw + 1e-6) / (tw.sum() + 1e-6)).numpy(), rtol=1e-12)
+    assert abs(tot - float(tw.sum())) < 1e-6
+
+
+def test_shard_rows_cover():
+    for S in (0, 1, 7, 10007, 131072):
+        for W in (1, 2, 3, 4, 8):
+            spans = [shard_rows(S, r, W) for r in range(W)]
+            assert spans[0][0] == 0 and spans[-1][1] == S
+            assert all(spans[i][1] == spans[i + 1][0] for i in range(W - 1))

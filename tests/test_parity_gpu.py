@@ -1,0 +1,267 @@
+"""GPU parity: every kernel variant against the CPU oracle and the golden
+fixtures, through the C ABI and through the torch operator."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (SENTINEL, bits_equal, first_mismatch, oracle_advantage, sha256_arrays,
+                     within_scan_tolerance)
+from pufferlib_b200.workloads import WORKLOADS, Workload, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+KEYS = ("values", "rewards", "dones", "importance")
+FORCE = {"tma2d": 1, "bulk1d": 2, "scan": 3, "generic": 4}
+
+
+@pytest.fixture(autouse=True)
+def _clear_force():
+    os.environ.pop("PUFF_ADV_FORCE_KERNEL", None)
+    os.environ.pop("PUFF_ADV_STAGES", None)
+    yield
+    os.environ.pop("PUFF_ADV_FORCE_KERNEL", None)
+    os.environ.pop("PUFF_ADV_STAGES", None)
+
+
+def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=SENTINEL, stages=None):
+    """Launch through the C ABI; returns (advantages, abs_sum or None, kernel name)."""
+    from pufferlib_b200 import cabi
+    from pufferlib_b200.advantage import launch_raw
+    dev = [torch.as_tensor(np.asarray(t)).contiguous().cuda() for t in inputs]
+    adv = torch.full_like(dev[0], sentinel)
+    abs_sum = torch.full((dev[0].shape[0],), -1.0, device="cuda") if epilogue else None
+    if force is not None:
+        os.environ["PUFF_ADV_FORCE_KERNEL"] = str(FORCE[force])
+    if stages is not None:
+        os.environ["PUFF_ADV_STAGES"] = str(stages)
+    try:
+        launch_raw(*dev, adv, *hyper, seg_abs_sum=abs_sum, variant=variant)
+        kernel = cabi.last_kernel()
+        torch.cuda.synchronize()
+    finally:
+        os.environ.pop("PUFF_ADV_FORCE_KERNEL", None)
+        os.environ.pop("PUFF_ADV_STAGES", None)
+    assert cabi.device_status() == 0
+    return adv.cpu().numpy(), None if abs_sum is None else abs_sum.cpu().numpy(), kernel
+
+
+def applicable(force, H):
+    if force == "tma2d":
+        return H % 4 == 0
+    return True
+
+
+# ---------------------------------------------------------------------------
+# golden fixtures (outputs of the reference CPU op)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("force", ["tma2d", "bulk1d", "generic"])
+def test_serial_kernels_match_golden_bitwise(golden_small, force):
+    ran = 0
+    for name, case in golden_small.items():
+        H = case["values"].shape[1]
+        if not applicable(force, H):
+            continue
+        got, _, kernel = run_gpu([case[k] for k in KEYS], case["hyper"], "serial", force)
+        if H >= 2:
+            assert kernel == force, (name, kernel)
+        assert bits_equal(got, case["advantages"]), f"{name}/{force}: {first_mismatch(got, case['advantages'])}"
+        ran += 1
+    assert ran >= 3
+
+
+def test_scan_kernel_matches_golden_within_tolerance(golden_small):
+    for name, case in golden_small.items():
+        if name in ("special", "odd127"):
+            continue   # non-finite inputs / |values| ~ 10: outside the scan variant's stated bar
+        got, _, kernel = run_gpu([case[k] for k in KEYS], case["hyper"], "scan")
+        want = case["advantages"]
+        assert np.all(got[:, -1] == np.float32(SENTINEL)), name
+        assert within_scan_tolerance(got[:, :-1], want[:, :-1]), name
+
+
+def test_scan_special_values_propagate(golden_small):
+    """NaN / Inf positions agree with the reference even where values differ in rounding."""
+    case = golden_small["special"]
+    got, _, _ = run_gpu([case[k] for k in KEYS], case["hyper"], "scan")
+    want = case["advantages"]
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    fin = np.isfinite(want)
+    np.testing.assert_allclose(got[fin], want[fin], rtol=1e-4, atol=1e-5)
+
+
+# ---------------------------------------------------------------------------
+# the five benchmark configurations
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["cfg0", "cfg1", "cfg2", "cfg3", "cfg4"])
+def test_config_serial_bitwise(name, config_digests):
+    wl = WORKLOADS[name]
+    inputs = [t.numpy() for t in make_inputs(wl)]
+    got, abs_sum, kernel = run_gpu(inputs, wl.hyper(), "serial", epilogue=True)
+    assert kernel == ("bulk1d" if wl.horizon % 4 else "tma2d")
+    want = oracle_advantage(inputs, wl.hyper())
+    assert bits_equal(got, want), f"{name}: {first_mismatch(got, want)}"
+    ref = config_digests["configs"][name]
+    if sha256_arrays(*inputs) == ref["inputs_sha256"]:
+        assert sha256_arrays(got) == ref["advantages_sha256"]
+    exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
+    np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["cfg0", "cfg1", "cfg2", "cfg3"])
+def test_config_scan_tolerance(name):
+    wl = WORKLOADS[name]
+    inputs = [t.numpy() for t in make_inputs(wl)]
+    got, abs_sum, kernel = run_gpu(inputs, wl.hyper(), "scan", epilogue=True)
+    assert kernel == "scan"
+    want = oracle_advantage(inputs, wl.hyper())
+    assert np.all(got[:, -1] == np.float32(SENTINEL))
+    assert within_scan_tolerance(got[:, :-1], want[:, :-1])
+    exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
+    np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6)
+
+
+def test_auto_variant_choices():
+    picks = {}
+    for name in ("cfg1", "cfg3", "cfg4"):
+        wl = WORKLOADS[name]
+        inputs = [t.numpy() for t in make_inputs(wl)]
+        _, _, picks[name] = run_gpu(inputs, wl.hyper(), "auto")
+    assert picks == {"cfg1": "tma2d", "cfg3": "scan", "cfg4": "bulk1d"}
+
+
+@pytest.mark.parametrize("stages", [2, 3, 4])
+def test_tma2d_stage_counts(stages):
+    wl = Workload("st", 1000, 200, seed=31, done_p=0.05)
+    inputs = [t.numpy() for t in make_inputs(wl)]
+    got, abs_sum, kernel = run_gpu(inputs, wl.hyper(), "serial", epilogue=True, stages=stages)
+    want = oracle_advantage(inputs, wl.hyper())
+    assert kernel == "tma2d" and bits_equal(got, want), first_mismatch(got, want)
+
+
+# ---------------------------------------------------------------------------
+# exhaustive small shapes, ragged tiles, canaries
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("force", ["tma2d", "bulk1d", "scan", "generic"])
+def test_small_shape_sweep(force):
+    rng_seed = 100
+    for S in (1, 2, 31, 32, 33, 65, 70):
+        for H in list(range(1, 41)) + [63, 64, 65, 68, 70, 96, 100, 127, 128, 129, 132]:
+            if not applicable(force, H):
+                continue
+            wl = Workload("sweep", S, H, seed=rng_seed, done_p=0.1)
+            rng_seed += 1
+            inputs = [t.numpy() for t in make_inputs(wl)]
+            variant = "scan" if force == "scan" else "serial"
+            got, abs_sum, kernel = run_gpu(inputs, wl.hyper(), variant, force, epilogue=True)
+            want = oracle_advantage(inputs, wl.hyper())
+            if force == "scan":
+                assert np.all(got[:, -1] == np.float32(SENTINEL)), (S, H)
+                assert within_scan_tolerance(got[:, :-1], want[:, :-1]), (S, H)
+            else:
+                assert bits_equal(got, want), f"S={S} H={H} {force}: {first_mismatch(got, want)}"
+            exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
+            np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6, err_msg=f"S={S} H={H}")
+
+
+@pytest.mark.parametrize("force,H", [("tma2d", 64), ("tma2d", 36), ("bulk1d", 91), ("bulk1d", 30),
+                                     ("scan", 64), ("scan", 333), ("generic", 17)])
+def test_canaries_around_buffers(force, H):
+    """Inputs and outputs live inside larger canary-filled allocations; nothing
+    outside advantages[:, :H-1] may change."""
+    from pufferlib_b200.advantage import launch_raw
+    S, pad = 77, 256
+    wl = Workload("canary", S, H, seed=41 + H)
+    host = make_inputs(wl)
+    n = S * H
+    bufs = [torch.full((n + 2 * pad,), 777.0, device="cuda") for _ in range(5)]
+    views = [b[pad:pad + n].view(S, H) for b in bufs]
+    for v, h in zip(views[:4], host):
+        v.copy_(h)
+    views[4].fill_(SENTINEL)
+    before = [b.clone() for b in bufs[:4]]
+    abs_buf = torch.full((S + 2 * pad,), 777.0, device="cuda")
+    os.environ["PUFF_ADV_FORCE_KERNEL"] = str(FORCE[force])
+    launch_raw(*views, *wl.hyper(), seg_abs_sum=abs_buf[pad:pad + S], variant="scan" if force == "scan" else "serial")
+    torch.cuda.synchronize()
+    for b, b0 in zip(bufs[:4], before):
+        assert torch.equal(b, b0)
+    out = bufs[4].cpu().numpy()
+    assert np.all(out[:pad] == 777.0) and np.all(out[pad + n:] == 777.0)
+    a = abs_buf.cpu().numpy()
+    assert np.all(a[:pad] == 777.0) and np.all(a[pad + S:] == 777.0)
+    adv = out[pad:pad + n].reshape(S, H)
+    assert np.all(adv[:, -1] == np.float32(SENTINEL))
+    want = oracle_advantage([t.numpy() for t in host], wl.hyper())
+    if force == "scan":
+        assert within_scan_tolerance(adv[:, :-1], want[:, :-1])
+    else:
+        assert bits_equal(adv, want), first_mismatch(adv, want)
+
+
+def test_misaligned_base_pointer_uses_generic():
+    """A view whose data pointer is only 4-byte aligned still works, bit-exactly."""
+    from pufferlib_b200 import cabi
+    from pufferlib_b200.advantage import launch_raw
+    wl = Workload("mis", 50, 64, seed=77)
+    host = make_inputs(wl)
+    n = 50 * 64
+    views = []
+    for h in host:
+        b = torch.zeros(n + 8, device="cuda")
+        v = b[1:1 + n].view(50, 64)
+        v.copy_(h)
+        views.append(v)
+    out = torch.full((n + 8,), SENTINEL, device="cuda")
+    adv = out[3:3 + n].view(50, 64)
+    launch_raw(*views, adv, *wl.hyper(), variant="serial")
+    assert cabi.last_kernel() == "generic"
+    want = oracle_advantage([t.numpy() for t in host], wl.hyper())
+    assert bits_equal(adv.cpu().numpy(), want)
+    launch_raw(*views, adv, *wl.hyper(), variant="scan")
+    assert cabi.last_kernel() == "scan"
+    assert within_scan_tolerance(adv.cpu().numpy()[:, :-1], want[:, :-1])
+
+
+# ---------------------------------------------------------------------------
+# size-independent properties at full size
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("name,variant", [("cfg2", "serial"), ("cfg4", "serial"), ("cfg3", "scan")])
+def test_power_of_two_scaling_is_exact(name, variant):
+    """The op is linear in (values, rewards): scaling both by 4 scales every
+    output by exactly 4 (a power of two commutes with fp32 rounding)."""
+    wl = WORKLOADS[name]
+    v, r, d, w = [t.numpy() for t in make_inputs(wl)]
+    base, _, _ = run_gpu([v, r, d, w], wl.hyper(), variant)
+    scaled, _, _ = run_gpu([v * 4, r * 4, d, w], wl.hyper(), variant)
+    assert bits_equal(scaled[:, :-1], base[:, :-1] * 4)
+
+
+def test_row_slices_equal_full_result():
+    """Rows are independent: any contiguous row block alone reproduces its
+    slice of the full result bit for bit (this is what sharding relies on)."""
+    wl = WORKLOADS["cfg2"].with_segments(20000)
+    inputs = [t.numpy() for t in make_inputs(wl)]
+    full, full_abs, _ = run_gpu(inputs, wl.hyper(), "serial", epilogue=True)
+    for lo, hi in ((0, 4999), (4999, 12345), (12345, 20000)):
+        part, part_abs, _ = run_gpu([a[lo:hi] for a in inputs], wl.hyper(), "serial", epilogue=True)
+        assert bits_equal(part, full[lo:hi])
+        assert bits_equal(part_abs, full_abs[lo:hi])
+
+
+def test_hyperparameter_edges():
+    wl = Workload("edge", 129, 64, seed=55, importance_sigma=1.0)
+    inputs = [t.numpy() for t in make_inputs(wl)]
+    for hyper in ((0.99, 0.95, 1.0, 0.0), (1.0, 1.0, 5.0, 5.0), (0.0, 0.95, 1.0, 1.0), (0.99, 0.0, 0.1, 0.1)):
+        want = oracle_advantage(inputs, hyper)
+        for force in ("tma2d", "bulk1d", "generic"):
+            got, _, _ = run_gpu(inputs, hyper, "serial", force)
+            assert bits_equal(got, want), (hyper, force, first_mismatch(got, want))
+        got, _, _ = run_gpu(inputs, hyper, "scan")
+        assert within_scan_tolerance(got[:, :-1], want[:, :-1]), hyper
+    ones = [inputs[0], inputs[1], np.ones_like(inputs[2]), inputs[3]]
+    want = oracle_advantage(ones, wl.hyper())
+    for variant in ("serial", "scan"):
+        got, _, _ = run_gpu(ones, wl.hyper(), variant)
+        assert bits_equal(got, want)   # all episodes end every step: no carry, so scan is exact too

@@ -1,0 +1,154 @@
+"""GPU: the torch operator boundary, the host-buffer entry point and the
+priority kernels."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import SENTINEL, bits_equal, first_mismatch, oracle_advantage
+from pufferlib_b200.workloads import WORKLOADS, Workload, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def test_op_in_place_contract_and_return():
+    import pufferlib_b200
+    wl = WORKLOADS["cfg0"]
+    host = make_inputs(wl)
+    dev = [t.cuda() for t in host]
+    adv = torch.full_like(dev[0], SENTINEL)
+    out = pufferlib_b200.compute_puff_advantage(*dev, adv, *wl.hyper())
+    assert out is adv
+    want = oracle_advantage([t.numpy() for t in host], wl.hyper())
+    assert bits_equal(adv.cpu().numpy(), want), first_mismatch(adv.cpu().numpy(), want)
+    for t, h in zip(dev, host):
+        assert torch.equal(t.cpu(), h)   # inputs are not modified despite the (a!) annotations
+
+
+def test_op_called_like_the_trainer():
+    """pufferl.py:352-356: zeros, call through torch.ops with python floats."""
+    from pufferlib_b200 import _C  # noqa: F401
+    wl = WORKLOADS["cfg1"]
+    host = make_inputs(wl)
+    values, rewards, terminals, ratio = [t.cuda() for t in host]
+    advantages = torch.zeros(values.shape, device="cuda")
+    r = torch.ops.pufferlib.compute_puff_advantage(values, rewards, terminals, ratio, advantages,
+                                                   0.99, 0.95, 1.0, 1.0)
+    assert r is None
+    want = oracle_advantage([t.numpy() for t in host], wl.hyper(), sentinel=0.0)
+    assert bits_equal(advantages.cpu().numpy(), want)
+
+
+def test_op_runs_on_the_current_stream():
+    import pufferlib_b200
+    wl = Workload("stream", 4096, 128, seed=5)
+    host = make_inputs(wl)
+    want = oracle_advantage([t.numpy() for t in host], wl.hyper())
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        dev = [t.cuda(non_blocking=True) for t in host]
+        adv = torch.full_like(dev[0], SENTINEL)
+        pufferlib_b200.compute_puff_advantage(*dev, adv, *wl.hyper())
+        got = adv.cpu()
+    side.synchronize()
+    assert bits_equal(got.numpy(), want)
+
+
+def test_op_rejects_bad_arguments():
+    import pufferlib_b200
+    wl = Workload("bad", 16, 32)
+    v, r, d, w = [t.cuda() for t in make_inputs(wl)]
+    adv = torch.zeros_like(v)
+    hyper = wl.hyper()
+    with pytest.raises(RuntimeError, match="contiguous"):
+        pufferlib_b200.compute_puff_advantage(v.t().contiguous().t(), r, d, w, adv, *hyper)
+    with pytest.raises(RuntimeError, match="float32"):
+        pufferlib_b200.compute_puff_advantage(v, r.double(), d, w, adv, *hyper)
+    with pytest.raises(RuntimeError, match="Second dimension"):
+        pufferlib_b200.compute_puff_advantage(v, r[:, :16].contiguous(), d, w, adv, *hyper)
+    with pytest.raises(RuntimeError, match="First dimension"):
+        pufferlib_b200.compute_puff_advantage(v, r, d[:8].contiguous(), w, adv, *hyper)
+    with pytest.raises(RuntimeError, match="2D"):
+        pufferlib_b200.compute_puff_advantage(v, r, d, w.reshape(-1), adv, *hyper)
+    with pytest.raises(RuntimeError, match="same device"):
+        pufferlib_b200.compute_puff_advantage(v, r, d, w, adv.cpu(), *hyper)
+    with pytest.raises(RuntimeError, match="overlap"):
+        pufferlib_b200.compute_puff_advantage(v, r, d, w, v, *hyper)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        pufferlib_b200.compute_puff_advantage(v.cpu(), r.cpu(), d.cpu(), w.cpu(), adv.cpu(), *hyper)
+    assert torch.all(adv == 0)
+
+
+def test_op_empty_and_degenerate_shapes():
+    import pufferlib_b200
+    for shape in ((0, 64), (5, 1), (0, 0), (3, 0)):
+        t = [torch.zeros(shape, device="cuda") for _ in range(4)]
+        adv = torch.full(shape, SENTINEL, device="cuda")
+        pufferlib_b200.compute_puff_advantage(*t, adv, 0.99, 0.95, 1.0, 1.0)
+        torch.cuda.synchronize()
+        assert torch.all(adv == SENTINEL)
+    s = torch.full((5,), 9.0, device="cuda")
+    t = [torch.zeros((5, 1), device="cuda") for _ in range(5)]
+    pufferlib_b200.compute_puff_advantage_prio(*t, s, 0.99, 0.95, 1.0, 1.0)
+    assert torch.all(s == 0)
+
+
+def test_meta_kernel_traces():
+    from pufferlib_b200 import _C  # noqa: F401
+    t = [torch.empty(8, 16, device="meta") for _ in range(5)]
+    torch.ops.pufferlib.compute_puff_advantage(*t, 0.99, 0.95, 1.0, 1.0)
+
+
+@pytest.mark.parametrize("name", ["cfg0", "cfg4", "cfg1"])
+def test_host_entry_point(name):
+    import pufferlib_b200
+    wl = WORKLOADS[name]
+    host = make_inputs(wl, pin=True)
+    adv = torch.full(host[0].shape, SENTINEL).pin_memory()
+    abs_sum = torch.full((wl.segments,), -1.0).pin_memory()
+    pufferlib_b200.compute_puff_advantage_host(*host, adv, *wl.hyper(), seg_abs_sum=abs_sum, variant="serial")
+    want = oracle_advantage([t.numpy() for t in host], wl.hyper())
+    assert bits_equal(adv.numpy(), want), first_mismatch(adv.numpy(), want)
+    exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
+    np.testing.assert_allclose(abs_sum.numpy(), exact, rtol=1e-5, atol=1e-6)
+
+
+def test_host_entry_point_many_blocks(monkeypatch):
+    """Small row blocks so that the slot ring wraps many times; pageable memory."""
+    import pufferlib_b200
+    monkeypatch.setenv("PUFF_HOST_BLOCK_BYTES", str(64 * 1024))
+    wl = Workload("blocks", 5000, 96, seed=8)
+    host = make_inputs(wl)
+    adv = torch.full(host[0].shape, SENTINEL)
+    pufferlib_b200.compute_puff_advantage_host(*host, adv, *wl.hyper())
+    want = oracle_advantage([t.numpy() for t in host], wl.hyper())
+    assert bits_equal(adv.numpy(), want), first_mismatch(adv.numpy(), want)
+    from pufferlib_b200 import cabi
+    assert cabi.load().puff_advantage_sm100_host_release(0) == 0
+
+
+@pytest.mark.parametrize("alpha", [0.8, 0.0, 1.0, 0.35])
+def test_priorities_match_oracle_and_torch(alpha):
+    import pufferlib_b200
+    from oracle import puff_oracle
+    wl = WORKLOADS["cfg4"]
+    host = make_inputs(wl)
+    dev = [t.cuda() for t in host]
+    adv = torch.zeros_like(dev[0])
+    adv, probs = pufferlib_b200.prioritized_sample_probs(*dev, adv, *wl.hyper(), alpha)
+    want = oracle_advantage([t.numpy() for t in host], wl.hyper(), sentinel=0.0)
+    w, p, tot = puff_oracle.priorities(puff_oracle.abs_sum(want), alpha)
+    np.testing.assert_allclose(probs.cpu().numpy(), p, rtol=2e-5)
+    # and the reference's own eager sequence (pufferl.py:359-361) on the same advantages
+    a = adv.abs().sum(axis=1)
+    pw = torch.nan_to_num(a ** alpha, 0, 0, 0)
+    pp = (pw + 1e-6) / (pw.sum() + 1e-6)
+    np.testing.assert_allclose(probs.cpu().numpy(), pp.cpu().numpy(), rtol=2e-5)
+    assert abs(float(probs.double().sum()) - 1.0) < 1e-3
+
+
+def test_priorities_non_finite_sums_become_zero_weight():
+    import pufferlib_b200
+    s = torch.tensor([1.0, float("nan"), float("inf"), 0.0, 2.0], device="cuda")
+    w, tot = pufferlib_b200.priority_weights(s, 0.5)
+    assert w.cpu().tolist() == pytest.approx([1.0, 0.0, 0.0, 0.0, 2.0 ** 0.5], rel=1e-6)
+    assert float(tot) == pytest.approx(1.0 + 2.0 ** 0.5, rel=1e-6)
