@@ -1,0 +1,433 @@
+#!/usr/bin/env python
+"""Benchmark of the advantage hot path: elements/s and achieved HBM GB/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl reference]
+
+A step is one pass of the path over one `[segments, horizon]` fp32 buffer that
+is already resident in HBM: the advantage kernel with its fused per-segment
+|advantage| sums, the priority weights, (N > 1) the all-reduce of the weight
+total, and the sampling probabilities.  With N GPUs every rank owns its own
+shard of `segments` rows (weak scaling: the global buffer has N x segments
+rows), exactly one process per GPU.
+
+One JSON line is printed by rank 0.  `value` is the whole-job rate with
+device-resident inputs, `e2e` the same metric through the host-buffer C-ABI
+entry point with pinned host inputs and outputs (copies inside the timed
+region), `roofline` the advantage kernel's algorithmic bytes over its
+CUDA-event duration against the measured HBM copy peak, and `cpu_baseline` the
+reference CPU op timed on this machine's cores.
+
+`--impl reference` times only the reference's own CPU implementation (the
+build under oracle/_ref/ when present, else the oracle port) and prints the
+same line shape.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from pufferlib_b200.workloads import WORKLOADS, make_inputs  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+BYTES_PER_ELEMENT = 20          # 4 fp32 inputs read + 1 fp32 output written
+PRIO_ALPHA = 0.8                # config/default.ini:60
+FALLBACK_HBM_GBS = 6650.0
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi in loop mode, read-only; samples are matched to the timed
+    windows by wall-clock time."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        self.path = None
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="puff_clocks_", suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "50", "-i", str(index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self, windows):
+        """windows: list of (t0, t1) wall-clock spans; returns the clocks dict."""
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        rows = []
+        try:
+            import datetime
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    rows.append((ts, float(parts[1]), float(parts[2]), parts[3], parts[5:9]))
+                except Exception:
+                    continue
+        finally:
+            try:
+                os.unlink(self.path)
+            except OSError:
+                pass
+        if not rows:
+            return None
+        inside = [r for r in rows if any(t0 <= r[0] <= t1 for t0, t1 in windows)]
+        scope = "timed region"
+        if not inside:
+            inside, scope = rows, "whole run (timed region shorter than the sampling period)"
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = sorted({n for r in inside for n, v in zip(names, r[4]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": inside[0][2],
+                "reasons": reasons, "samples": len(inside), "scope": scope}
+
+
+# ---------------------------------------------------------------------------
+# reference / CPU arm
+# ---------------------------------------------------------------------------
+def cpu_reference_rate(wl, seconds_budget, want_single=True):
+    """Elements/s of the reference CPU op on this machine: as shipped (one
+    thread) and from a thread pool over contiguous row slices on all physical
+    cores (the op has no internal parallelism; torch releases the GIL)."""
+    import numpy as np
+    import psutil
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import puff_oracle
+
+    ref = puff_oracle.load_reference()
+    kind = "reference" if ref is not None else "port"
+    inputs = make_inputs(wl)
+    adv = torch.zeros_like(inputs[0])
+    hyper = wl.hyper()
+    S, H = wl.segments, wl.horizon
+    torch.set_num_threads(1)
+
+    if ref is not None:
+        def run_rows(lo, hi):
+            ref(*[t[lo:hi] for t in inputs], adv[lo:hi], *hyper)
+    else:
+        np_in = [t.numpy() for t in inputs]
+        np_adv = adv.numpy()
+
+        def run_rows(lo, hi):
+            puff_oracle.advantage(*[a[lo:hi] for a in np_in], np_adv[lo:hi], *hyper)
+
+    # one thread, a slice worth ~0.25 s
+    single = None
+    if want_single:
+        rows1 = max(1, min(S, int(30e6) // H))
+        run_rows(0, min(rows1, 1024))
+        t0 = time.perf_counter()
+        run_rows(0, rows1)
+        single = rows1 * H / (time.perf_counter() - t0)
+
+    cores = psutil.cpu_count(logical=False) or os.cpu_count() or 1
+    try:
+        cores = min(cores, len(os.sched_getaffinity(0)))
+    except Exception:
+        pass
+    bounds = [((i * S) // cores, ((i + 1) * S) // cores) for i in range(cores)]
+    times = []
+    with ThreadPoolExecutor(max_workers=cores) as pool:
+        list(pool.map(lambda b: run_rows(*b), bounds))   # warm
+        t_end = time.perf_counter() + seconds_budget
+        while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 50):
+            t0 = time.perf_counter()
+            list(pool.map(lambda b: run_rows(*b), bounds))
+            times.append(time.perf_counter() - t0)
+    pooled = S * H / statistics.median(times)
+    return {"kind": kind, "cores": cores, "pooled": pooled, "single": single, "passes": len(times),
+            "sample": f"{len(times)} full passes over {S}x{H} from {cores} threads over row slices"
+                      + (f"; 1 thread on {rows1}x{H}" if want_single else "")}
+
+
+def run_reference_arm(args, wl, rank, world):
+    if rank != 0:
+        return
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    # bound the whole run: every step is one pooled pass over a sample of the workload
+    import psutil
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import puff_oracle
+    ref = puff_oracle.load_reference()
+    kind = "reference" if ref is not None else "port"
+    cores = psutil.cpu_count(logical=False) or os.cpu_count() or 1
+    try:
+        cores = min(cores, len(os.sched_getaffinity(0)))
+    except Exception:
+        pass
+    torch.set_num_threads(1)
+    budget = 90.0 / (steps + warmup)
+    rows = int(min(wl.segments, max(cores * 8, budget * 100e6 * max(1, cores // 2) / wl.horizon)))
+    sample = wl.with_segments(rows)
+    inputs = make_inputs(sample)
+    adv = torch.zeros_like(inputs[0])
+    hyper = wl.hyper()
+    if ref is not None:
+        def run_rows(b):
+            ref(*[t[b[0]:b[1]] for t in inputs], adv[b[0]:b[1]], *hyper)
+    else:
+        np_in = [t.numpy() for t in inputs]
+        np_adv = adv.numpy()
+
+        def run_rows(b):
+            puff_oracle.advantage(*[a[b[0]:b[1]] for a in np_in], np_adv[b[0]:b[1]], *hyper)
+    bounds = [((i * rows) // cores, ((i + 1) * rows) // cores) for i in range(cores)]
+    with ThreadPoolExecutor(max_workers=cores) as pool:
+        for _ in range(warmup):
+            list(pool.map(run_rows, bounds))
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            list(pool.map(run_rows, bounds))
+        dt = time.perf_counter() - t0
+    t1 = time.perf_counter()
+    run_rows((0, max(1, rows // cores)))
+    single = max(1, rows // cores) * wl.horizon / (time.perf_counter() - t1)
+    value = rows * wl.horizon * steps / dt
+    line = {
+        "impl": "reference", "metric": "advantage elements/sec", "value": value, "unit": "elements/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": 1e3 * dt / steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": workload_config(wl, args.gpus, "reference CPU op"),
+        "cpu_baseline": {"value": value, "unit": "elements/s", "cores": cores, "kind": kind,
+                         "sample": f"each step: one pass over the first {rows} of {wl.segments} segments x {wl.horizon}, "
+                                   f"row slices on {cores} threads (the op itself is single-threaded)",
+                         "single_thread_value": single},
+        "e2e": {"value": value, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "achieved_gbs": value * BYTES_PER_ELEMENT / 1e9,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(wl, n_gpus, what):
+    return {"workload": f"{wl.name}: {wl.segments}x{wl.horizon} fp32 per GPU ({what})",
+            "segments_per_gpu": wl.segments, "horizon": wl.horizon,
+            "global_segments": wl.segments * n_gpus,
+            "gamma": wl.gamma, "lambda": wl.lam, "rho_clip": wl.rho_clip, "c_clip": wl.c_clip,
+            "parallelism": f"segments sharded over {n_gpus} GPU(s), one scalar all-reduce per step"
+                           if n_gpus > 1 else "single GPU"}
+
+
+# ---------------------------------------------------------------------------
+# the B200 arm
+# ---------------------------------------------------------------------------
+def run_b200_arm(args, wl, rank, local_rank, world):
+    import torch.distributed as dist
+    import pufferlib_b200
+    from pufferlib_b200 import cabi
+    from pufferlib_b200.sharded import ShardedAdvantage
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the B200 arm has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    S, H = wl.segments, wl.horizon
+    hyper = wl.hyper()
+    elems = S * H
+    set_bytes = BYTES_PER_ELEMENT * elems
+    # inputs larger than L2: either one buffer set already is, or rotate over enough sets
+    n_sets = 1 if set_bytes >= 2 * L2_BYTES else -(-2 * L2_BYTES // set_bytes)
+    host = make_inputs(wl.with_segments(S, seed=wl.seed + rank), pin=True)
+    sets = []
+    for i in range(n_sets):
+        ins = [t.to(dev) for t in host] if i == 0 else [t.clone() for t in sets[0][:4]]
+        sets.append(ins + [torch.zeros((S, H), device=dev), torch.empty(S, device=dev)])
+    sharded = ShardedAdvantage(S * world, H, hyper, PRIO_ALPHA, rank=rank, world=world)
+    variant = args.variant
+    os.environ["PUFFER_ADV_VARIANT"] = variant
+
+    def step(i, ev=None):
+        v, r, d, w, adv, abs_sum = sets[i % n_sets]
+        if ev is not None:
+            ev[0].record()
+        sharded.kernels.advantage_prio(v, r, d, w, adv, abs_sum, hyper)
+        if ev is not None:
+            ev[1].record()
+        weights, total = sharded.kernels.weights(abs_sum, PRIO_ALPHA)
+        if world > 1:
+            dist.all_reduce(total)
+        return sharded.kernels.probs(weights, total)
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+    for i in range(warmup):
+        step(i)
+    kernel_name = cabi.last_kernel()
+    fence()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    windows = []
+
+    # ---- device-resident timing -------------------------------------------
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = cabi.launch_count()
+    fence()
+    w0 = time.time()
+    t_start.record()
+    for i in range(steps):
+        probs = step(i, kev[i])
+    t_stop.record()
+    fence()
+    windows.append((w0, time.time()))
+    launches = cabi.launch_count() - launches0
+    ms_total = t_start.elapsed_time(t_stop)
+    kernel_ms = sum(a.elapsed_time(b) for a, b in kev) / steps
+    if world > 1:
+        t = torch.tensor([ms_total, kernel_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, kernel_ms = float(t[0]), float(t[1])
+    value = elems * world * steps / (ms_total * 1e-3)
+
+    # ---- kernel-only loop (no events between launches, no priorities) -------
+    ko_steps = steps
+    fence()
+    t_start.record()
+    for i in range(ko_steps):
+        v, r, d, w, adv, abs_sum = sets[i % n_sets]
+        sharded.kernels.advantage_prio(v, r, d, w, adv, abs_sum, hyper)
+    t_stop.record()
+    fence()
+    ko_ms = t_start.elapsed_time(t_stop) / ko_steps
+    if world > 1:
+        t = torch.tensor([ko_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ko_ms = float(t[0])
+
+    # ---- end to end through the host-buffer C ABI ----------------------------
+    e2e_steps = max(2, min(steps, args.e2e_steps))
+    h_adv = torch.zeros((S, H)).pin_memory()
+    h_abs = torch.zeros(S).pin_memory()
+    for _ in range(2):
+        pufferlib_b200.compute_puff_advantage_host(*host, h_adv, *hyper, seg_abs_sum=h_abs,
+                                                   variant=variant, device=local_rank)
+    fence()
+    w0 = time.time()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        pufferlib_b200.compute_puff_advantage_host(*host, h_adv, *hyper, seg_abs_sum=h_abs,
+                                                   variant=variant, device=local_rank)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    fence()
+    windows.append((w0, time.time()))
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t[0])
+    e2e_value = elems * world * e2e_steps / e2e_s
+
+    clocks = sampler.stop(windows) if sampler is not None else None
+
+    if rank == 0:
+        peak, peak_kind = hbm_peak()
+        achieved = BYTES_PER_ELEMENT * elems / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": "advantage elements/sec", "value": value, "unit": "elements/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_total / steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": dict(workload_config(wl, world, f"variant {variant}, kernel {kernel_name}"),
+                           l2="inputs larger than L2" if n_sets == 1 else
+                              f"rotating over {n_sets} buffer sets ({n_sets * set_bytes >> 20} MiB > 2x L2)"),
+            "achieved_gbs": value * BYTES_PER_ELEMENT / 1e9,
+            "kernel_only": {"ms_per_launch": ko_ms, "elements_per_s": elems * world / (ko_ms * 1e-3),
+                            "gbs_per_gpu": BYTES_PER_ELEMENT * elems / (ko_ms * 1e-3) / 1e9},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": TRAFFIC.get((wl.name, kernel_name)),
+                         "kernel": kernel_name, "kernel_ms": kernel_ms, "peak_kind": f"of {peak_kind}",
+                         "algorithmic_bytes": BYTES_PER_ELEMENT * elems},
+            "e2e": {"value": e2e_value, "unit": "elements/s", "h2d_bytes_per_step": 16 * elems * world,
+                    "d2h_bytes_per_step": (4 * S * (H - 1) + 4 * S) * world, "steps": e2e_steps,
+                    "ms_per_step": 1e3 * e2e_s / e2e_steps,
+                    "api": "puff_advantage_sm100_host (C ABI, pinned host buffers)"},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            cpu = cpu_reference_rate(wl, seconds_budget=6.0)
+            line["cpu_baseline"] = {"value": cpu["pooled"], "unit": "elements/s", "cores": cpu["cores"],
+                                    "kind": cpu["kind"], "sample": cpu["sample"],
+                                    "single_thread_value": cpu["single"]}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the
+# ncu captures summarised under profiles/; None until a capture exists.
+TRAFFIC = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--variant", default="auto", choices=["auto", "serial", "scan", "generic"])
+    ap.add_argument("--e2e-steps", type=int, default=20)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, wl, rank, world)
+        return
+    if args.gpus > 1 and world == 1:
+        raise SystemExit("launch with torchrun: python -m torch.distributed.run --nnodes=1 "
+                         f"--nproc-per-node {args.gpus} --master-addr 127.0.0.1 bench.py --gpus {args.gpus}")
+    run_b200_arm(args, wl, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -53,7 +53,8 @@ constexpr int kTileRows = 32;              // segments per warp tile
 constexpr int kChunkCols = 32;             // columns per TMA box (128 bytes)
 constexpr int kBoxBytes = kTileRows * kChunkCols * 4;   // 4096
 constexpr int kStageBytes = 4 * kBoxBytes;              // v, r, d, w
-constexpr uint32_t kWaitLimit = 1u << 24;  // mbarrier polls before giving up
+constexpr uint32_t kWaitLimit = 1u << 24;             // mbarrier polls before giving up ...
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // ... or two seconds, whichever comes first
 
 // ---------------------------------------------------------------------------
 // the recurrence step, in the reference's operation order
@@ -114,14 +115,23 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok;
 }
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 // Bounded wait; returns true when every lane of the warp saw the phase flip.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity)
 {
     uint32_t ok = mbar_try_wait(bar, parity);
-    uint32_t polls = 0;
-    while (!ok && polls < kWaitLimit) {
-        ok = mbar_try_wait(bar, parity);
-        ++polls;
+    if (!ok) {
+        const unsigned long long t0 = global_ns();
+        uint32_t polls = 0;
+        while (!ok && polls < kWaitLimit) {
+            ok = mbar_try_wait(bar, parity);
+            if ((++polls & 1023u) == 0u && global_ns() - t0 > kWaitLimitNs) break;
+        }
     }
     return __all_sync(0xffffffffu, ok != 0);
 }

@@ -1,0 +1,74 @@
+"""Segment-sharded advantage + prioritised-replay weights over several GPUs.
+
+Segments (rows) are independent, so a buffer of `segments x horizon` shards by
+contiguous row blocks with no data-path communication; the only exchange is
+the all-reduce of one fp64 scalar, the total priority weight that
+pufferl.py:361 divides by.  The reference itself never shards this op (its DDP
+ranks own private buffers, pufferl.py:913-939); this class is the layout the
+multi-GPU benchmark measures: one process per GPU, `torch.distributed` for
+the scalar.
+
+`kernels` is the object that provides the three device steps.  The default is
+the CUDA implementation; tests of the host-side logic on CPU ranks pass a
+stand-in with the same three methods.
+"""
+import torch
+import torch.distributed as dist
+
+from .workloads import shard_rows
+
+
+class CudaKernels:
+    """The product path: the sm_100a kernels behind torch.ops.pufferlib."""
+
+    def __init__(self):
+        from . import advantage
+        self._adv = advantage
+
+    def advantage_prio(self, values, rewards, dones, importance, advantages, seg_abs_sum, hyper):
+        self._adv.compute_puff_advantage_prio(values, rewards, dones, importance, advantages,
+                                              seg_abs_sum, *hyper)
+
+    def weights(self, seg_abs_sum, alpha):
+        return self._adv.priority_weights(seg_abs_sum, alpha)
+
+    def probs(self, weights, total):
+        return self._adv.priority_probs(weights, total)
+
+
+class ShardedAdvantage:
+    """One rank's shard of the advantage path.
+
+    step() computes advantages for the local rows, the local priority weights,
+    all-reduces their total over `group`, and returns the local slice of the
+    globally normalised sampling probabilities."""
+
+    def __init__(self, global_segments, horizon, hyper, prio_alpha, group=None, kernels=None,
+                 rank=None, world=None):
+        self.group = group
+        if rank is None:
+            rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if world is None:
+            world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank, self.world = rank, world
+        self.lo, self.hi = shard_rows(global_segments, rank, world)
+        self.global_segments = global_segments
+        self.horizon = horizon
+        self.hyper = tuple(hyper)
+        self.prio_alpha = prio_alpha
+        self.kernels = kernels if kernels is not None else CudaKernels()
+
+    @property
+    def local_segments(self):
+        return self.hi - self.lo
+
+    def step(self, values, rewards, dones, importance, advantages, seg_abs_sum):
+        """All tensors are this rank's rows [local_segments, horizon] (and
+        [local_segments] for seg_abs_sum).  Returns (probs, total) where total
+        is the global weight sum as a 1-element fp64 tensor."""
+        k = self.kernels
+        k.advantage_prio(values, rewards, dones, importance, advantages, seg_abs_sum, self.hyper)
+        weights, total = k.weights(seg_abs_sum, self.prio_alpha)
+        if self.world > 1:
+            dist.all_reduce(total, op=dist.ReduceOp.SUM, group=self.group)
+        return k.probs(weights, total), total
