@@ -14,6 +14,7 @@ Both land next to this file so that the package works from the source tree.
 Outputs are rebuilt only when a source is newer.
 """
 import os
+import shutil
 import subprocess
 import sys
 import sysconfig
@@ -35,6 +36,20 @@ NVCC_FLAGS = [
     "--ftz=false", "--prec-div=true", "--prec-sqrt=true", "--fmad=true",
     "-Xcompiler", "-fPIC", "-shared",
 ]
+
+
+def _host_cxx():
+    """The system g++.  A compiler wrapper that points the linker at a static
+    libstdc++ (as the CXX of some build images does) would embed a second,
+    uninitialised copy of the C++ runtime in the module; its iostreams crash
+    the first time an error message formats a number."""
+    override = os.environ.get("PUFF_CXX")
+    if override:
+        return override
+    for cand in ("/usr/bin/g++", shutil.which("g++"), os.environ.get("CXX")):
+        if cand and os.path.exists(cand):
+            return cand
+    return "g++"
 
 
 def _stale(target, sources):
@@ -67,7 +82,7 @@ def build_torch_ext(force=False, verbose=False):
     src = os.path.join(CSRC, "torch_binding.cpp")
     deps = [src, os.path.join(INCLUDE, "puff_advantage.h"), CABI_LIB]
     if force or _stale(TORCH_EXT, deps):
-        cxx = os.environ.get("CXX", "g++")
+        cxx = _host_cxx()
         inc = [f"-I{p}" for p in include_paths()]
         inc += [f"-I{os.path.join(CUDA_HOME, 'include')}", f"-I{sysconfig.get_paths()['include']}"]
         libdir = library_paths()[0]

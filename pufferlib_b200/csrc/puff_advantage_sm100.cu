@@ -15,10 +15,11 @@
 //           chunk of the four inputs arrives as a 32x32 TMA box in
 //           128B-swizzled shared memory behind an mbarrier ring, lane r runs
 //           row r's recurrence out of shared memory with conflict-free 128-bit
-//           reads, and the advantages leave through a TMA store whose tensor
-//           map is one column narrower than the row, so the hardware's bounds
-//           clipping keeps advantages[:, H-1] untouched.  Needs H % 4 == 0 and
-//           16-byte aligned base pointers.
+//           reads, and the advantages leave through a TMA store.  TMA clips a
+//           store at the tensor edge in whole 16-byte units only, so column
+//           H-1 cannot be masked out of the box: each lane reads its row's
+//           advantages[H-1] once per tile and the store writes that same value
+//           back.  Needs H % 4 == 0 and 16-byte aligned base pointers.
 //   bulk1d  serial, bit-exact, for H % 4 != 0 (row pitch not a multiple of
 //           16 bytes, so no 2-D tensor map exists): tiles of 4..32 whole rows
 //           are contiguous spans, fetched with 1-D bulk copies.
@@ -214,8 +215,8 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
                       const __grid_constant__ CUtensorMap tm_d,
                       const __grid_constant__ CUtensorMap tm_w,
                       const __grid_constant__ CUtensorMap tm_a,
-                      float* __restrict__ seg_abs_sum, float gamma, float lambda, float rho_clip,
-                      float c_clip, long long num_segments, int horizon, int num_tiles)
+                      const float* adv_in, float* __restrict__ seg_abs_sum, float gamma, float lambda,
+                      float rho_clip, float c_clip, long long num_segments, int horizon, int num_tiles)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -269,21 +270,24 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
 
     float a_run = 0.0f, abs_run = 0.0f;
     float nv = 0.0f, nr = 0.0f, nd = 0.0f;   // values/rewards/dones at column t+1 across units
+    float keep_last = 0.0f;                  // the caller's advantages[row, H-1]
     int k = 0, c = nchunks - 1, s = 0;
     uint32_t parity = 0;
     bool failed = false;
 
     for (int i = 0; i < total; ++i) {
+        if (c == nchunks - 1) {   // new tile
+            const long long row = (static_cast<long long>(blockIdx.x) + static_cast<long long>(k) * gridDim.x) * kTileRows + lane;
+            keep_last = row < num_segments ? adv_in[row * horizon + horizon - 1] : 0.0f;
+            a_run = 0.0f;
+            abs_run = 0.0f;
+        }
         // the output box i&1 was last read by the store of item i-2
         if (lane == 0) bulk_wait_read<1>();
         __syncwarp();
         if (!mbar_wait_warp(bar_base + 8 * s, parity)) {
             failed = true;
             break;
-        }
-        if (c == nchunks - 1) {
-            a_run = 0.0f;
-            abs_run = 0.0f;
         }
         const uint32_t st = base + s * kStageBytes;
         const uint32_t ob = out_base + (i & 1) * kBoxBytes;
@@ -298,12 +302,15 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
                 const float4 d4 = lds128(st + 2 * kBoxBytes + off);
                 const float4 w4 = lds128(st + 3 * kBoxBytes + off);
                 float4 a4;
-                // column col0+3 is H-1 in the last unit of a row: no step there
+                // column col0+3 is H-1 in the last unit of a row: no step there,
+                // the caller's value goes back unchanged
                 if (col0 + 4 < horizon) {
                     a_run = adv_step(v4.w, w4.w, nv, nr, nd, a_run, gamma, gl, rho_clip, c_clip);
                     if (EPI) abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                    a4.w = a_run;
+                } else {
+                    a4.w = keep_last;
                 }
-                a4.w = a_run;
                 a_run = adv_step(v4.z, w4.z, v4.w, r4.w, d4.w, a_run, gamma, gl, rho_clip, c_clip);
                 if (EPI) abs_run = __fadd_rn(abs_run, fabsf(a_run));
                 a4.z = a_run;
@@ -807,12 +814,12 @@ static cudaError_t launch_tma2d(const MapSet& m, float* seg_abs_sum, float gamma
 {
     if (seg_abs_sum != nullptr)
         puff_adv_tma2d_kernel<NST, true><<<grid, 32, tma2d_smem_bytes<NST>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], seg_abs_sum, gamma, lambda, rho_clip, c_clip, rows,
-            horizon, tiles);
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[4], seg_abs_sum, gamma, lambda, rho_clip, c_clip,
+            rows, horizon, tiles);
     else
         puff_adv_tma2d_kernel<NST, false><<<grid, 32, tma2d_smem_bytes<NST>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], nullptr, gamma, lambda, rho_clip, c_clip, rows,
-            horizon, tiles);
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[4], nullptr, gamma, lambda, rho_clip, c_clip,
+            rows, horizon, tiles);
     return cudaGetLastError();
 }
 
@@ -938,10 +945,8 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
             for (int i = 0; i < 5 && hit; ++i) hit = cache.ptr[i] == p[i];
             if (!hit) {
                 cache.rows = -1;
-                for (int i = 0; i < 4; ++i)
+                for (int i = 0; i < 5; ++i)
                     if (!make_map(&cache.tm[i], p[i], rows, horizon, horizon)) return PUFF_ERR_DRIVER;
-                // one column narrower: stores to column H-1 are clipped by the hardware
-                if (!make_map(&cache.tm[4], p[4], rows, horizon - 1, horizon)) return PUFF_ERR_DRIVER;
                 for (int i = 0; i < 5; ++i) cache.ptr[i] = p[i];
                 cache.rows = rows;
                 cache.horizon = horizon;

@@ -78,13 +78,16 @@ void compute_puff_advantage_cuda(torch::Tensor values, torch::Tensor rewards, to
                                  double lambda, double rho_clip, double c_clip)
 {
     check_inputs({values, rewards, dones, importance, advantages}, values);
-    const c10::cuda::CUDAGuard guard(values.device());
-    const int rc = puff_advantage_sm100_launch(
-        values.data_ptr<float>(), rewards.data_ptr<float>(), dones.data_ptr<float>(),
-        importance.data_ptr<float>(), advantages.data_ptr<float>(), nullptr,
-        static_cast<float>(gamma), static_cast<float>(lambda), static_cast<float>(rho_clip),
-        static_cast<float>(c_clip), values.size(0), values.size(1), variant_from_env(),
-        at::cuda::getCurrentCUDAStream().stream());
+    int rc;
+    {
+        const c10::cuda::CUDAGuard guard(values.device());
+        rc = puff_advantage_sm100_launch(
+            values.data_ptr<float>(), rewards.data_ptr<float>(), dones.data_ptr<float>(),
+            importance.data_ptr<float>(), advantages.data_ptr<float>(), nullptr,
+            static_cast<float>(gamma), static_cast<float>(lambda), static_cast<float>(rho_clip),
+            static_cast<float>(c_clip), values.size(0), values.size(1), variant_from_env(),
+            at::cuda::getCurrentCUDAStream().stream());
+    }
     check_rc(rc, "compute_puff_advantage");
 }
 
@@ -102,13 +105,16 @@ void compute_puff_advantage_prio_cuda(torch::Tensor values, torch::Tensor reward
     TORCH_CHECK(seg_abs_sum.device() == values.device(), "All tensors must be on same device");
     TORCH_CHECK(seg_abs_sum.dtype() == torch::kFloat32, "All tensors must be float32");
     TORCH_CHECK(seg_abs_sum.is_contiguous(), "All tensors must be contiguous");
-    const c10::cuda::CUDAGuard guard(values.device());
-    const int rc = puff_advantage_sm100_launch(
-        values.data_ptr<float>(), rewards.data_ptr<float>(), dones.data_ptr<float>(),
-        importance.data_ptr<float>(), advantages.data_ptr<float>(), seg_abs_sum.data_ptr<float>(),
-        static_cast<float>(gamma), static_cast<float>(lambda), static_cast<float>(rho_clip),
-        static_cast<float>(c_clip), values.size(0), values.size(1), variant_from_env(),
-        at::cuda::getCurrentCUDAStream().stream());
+    int rc;
+    {
+        const c10::cuda::CUDAGuard guard(values.device());
+        rc = puff_advantage_sm100_launch(
+            values.data_ptr<float>(), rewards.data_ptr<float>(), dones.data_ptr<float>(),
+            importance.data_ptr<float>(), advantages.data_ptr<float>(), seg_abs_sum.data_ptr<float>(),
+            static_cast<float>(gamma), static_cast<float>(lambda), static_cast<float>(rho_clip),
+            static_cast<float>(c_clip), values.size(0), values.size(1), variant_from_env(),
+            at::cuda::getCurrentCUDAStream().stream());
+    }
     check_rc(rc, "compute_puff_advantage_prio");
 }
 
