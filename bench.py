@@ -337,27 +337,33 @@ def run_b200_arm(args, wl, rank, local_rank, world):
         ko_ms = float(t[0])
 
     # ---- end to end through the host-buffer C ABI ----------------------------
-    e2e_steps = max(2, min(steps, args.e2e_steps))
-    h_adv = torch.zeros((S, H)).pin_memory()
-    h_abs = torch.zeros(S).pin_memory()
-    for _ in range(2):
-        pufferlib_b200.compute_puff_advantage_host(*host, h_adv, *hyper, seg_abs_sum=h_abs,
-                                                   variant=variant, device=local_rank)
-    fence()
-    w0 = time.time()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        pufferlib_b200.compute_puff_advantage_host(*host, h_adv, *hyper, seg_abs_sum=h_abs,
-                                                   variant=variant, device=local_rank)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    fence()
-    windows.append((w0, time.time()))
-    if world > 1:
-        t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t[0])
-    e2e_value = elems * world * e2e_steps / e2e_s
+    e2e = None
+    if args.e2e_steps > 0:
+        e2e_steps = max(2, min(steps, args.e2e_steps))
+        h_adv = torch.zeros((S, H)).pin_memory()
+        h_abs = torch.zeros(S).pin_memory()
+        for _ in range(2):
+            pufferlib_b200.compute_puff_advantage_host(*host, h_adv, *hyper, seg_abs_sum=h_abs,
+                                                       variant=variant, device=local_rank)
+        fence()
+        w0 = time.time()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            pufferlib_b200.compute_puff_advantage_host(*host, h_adv, *hyper, seg_abs_sum=h_abs,
+                                                       variant=variant, device=local_rank)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        fence()
+        windows.append((w0, time.time()))
+        if world > 1:
+            t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t[0])
+        e2e = {"value": elems * world * e2e_steps / e2e_s, "unit": "elements/s",
+               "h2d_bytes_per_step": 16 * elems * world,
+               "d2h_bytes_per_step": (4 * S * (H - 1) + 4 * S) * world, "steps": e2e_steps,
+               "ms_per_step": 1e3 * e2e_s / e2e_steps,
+               "api": "puff_advantage_sm100_host (C ABI, pinned host buffers)"}
 
     clocks = sampler.stop(windows) if sampler is not None else None
 
@@ -379,10 +385,7 @@ def run_b200_arm(args, wl, rank, local_rank, world):
                          "frac": achieved / peak, "traffic": TRAFFIC.get((wl.name, kernel_name)),
                          "kernel": kernel_name, "kernel_ms": kernel_ms, "peak_kind": f"of {peak_kind}",
                          "algorithmic_bytes": BYTES_PER_ELEMENT * elems},
-            "e2e": {"value": e2e_value, "unit": "elements/s", "h2d_bytes_per_step": 16 * elems * world,
-                    "d2h_bytes_per_step": (4 * S * (H - 1) + 4 * S) * world, "steps": e2e_steps,
-                    "ms_per_step": 1e3 * e2e_s / e2e_steps,
-                    "api": "puff_advantage_sm100_host (C ABI, pinned host buffers)"},
+            "e2e": e2e,
             "gpu_launches": launches,
             "clocks": clocks,
         }
@@ -412,6 +415,8 @@ def main():
     ap.add_argument("--variant", default="auto", choices=["auto", "serial", "scan", "generic"])
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--segments", type=int, default=0,
+                    help="override the workload's segment count (small cases for profiler captures)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -420,6 +425,8 @@ def main():
     if world != args.gpus and world > 1:
         args.gpus = world
     wl = WORKLOADS[args.workload]
+    if args.segments > 0:
+        wl = wl.with_segments(args.segments)
     if args.impl == "reference":
         run_reference_arm(args, wl, rank, world)
         return

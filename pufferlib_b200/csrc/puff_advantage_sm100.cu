@@ -78,6 +78,21 @@ __device__ __forceinline__ float adv_step(float v_t, float w_t, float v_n, float
     return __fadd_rn(delta, carry);
 }
 
+// The part of a step that does not depend on the running advantage:
+//   delta = rho * ((r' + (gamma*v')*nn) - v),  gc = (gamma*lambda)*c,  nn = 1 - d'
+// so that A = delta + (gc * A_next) * nn reproduces adv_step() bit for bit.
+__device__ __forceinline__ void adv_terms(float v_t, float w_t, float v_n, float r_n, float d_n,
+                                          float gamma, float gl, float rho_clip, float c_clip,
+                                          float& delta, float& gc, float& nn)
+{
+    nn = __fsub_rn(1.0f, d_n);
+    const float rho = fminf(w_t, rho_clip);
+    const float c = fminf(w_t, c_clip);
+    const float td = __fsub_rn(__fadd_rn(r_n, __fmul_rn(__fmul_rn(gamma, v_n), nn)), v_t);
+    delta = __fmul_rn(rho, td);
+    gc = __fmul_rn(gl, c);
+}
+
 // ---------------------------------------------------------------------------
 // PTX wrappers: mbarrier, TMA (non-multicast), bulk groups
 // ---------------------------------------------------------------------------
@@ -181,7 +196,8 @@ __device__ __forceinline__ float4 lds128(uint32_t addr)
     float4 v;
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "r"(addr));
+                 : "r"(addr)
+                 : "memory");
     return v;
 }
 __device__ __forceinline__ void sts128(uint32_t addr, float4 v)
@@ -189,6 +205,145 @@ __device__ __forceinline__ void sts128(uint32_t addr, float4 v)
     asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
                  "f"(v.w)
                  : "memory");
+}
+
+
+// ---------------------------------------------------------------------------
+// one 32-column chunk of one row, out of a 128B-swizzled stage
+// ---------------------------------------------------------------------------
+// sum of |x[j]| in a fixed pairwise order
+__device__ __forceinline__ float abs_tree32(const float (&x)[32])
+{
+    float t[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) t[j] = __fadd_rn(fabsf(x[2 * j + 1]), fabsf(x[2 * j]));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = __fadd_rn(t[2 * j + 1], t[2 * j]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) t[j] = __fadd_rn(t[2 * j + 1], t[2 * j]);
+    return __fadd_rn(__fadd_rn(t[3], t[2]), __fadd_rn(t[1], t[0]));
+}
+
+// Literal path: the reference's operation order step by step, any H % 4 == 0,
+// columns at or beyond H-1 skipped (the advantage stays what it was).
+__device__ __forceinline__ void chunk_literal(uint32_t st, uint32_t row_off, uint32_t sw, int cbase, int horizon,
+                                              float gamma, float gl, float rho_clip, float c_clip,
+                                              float& a_run, float& nv, float& nr, float& nd, float (&out)[32])
+{
+#pragma unroll
+    for (int q = 7; q >= 0; --q) {
+        const int col0 = cbase + 4 * q;
+        out[4 * q] = out[4 * q + 1] = out[4 * q + 2] = out[4 * q + 3] = 0.0f;
+        if (col0 < horizon) {   // warp-uniform
+            const uint32_t off = row_off + ((static_cast<uint32_t>(q) ^ sw) << 4);
+            const float4 v4 = lds128(st + 0 * kBoxBytes + off);
+            const float4 r4 = lds128(st + 1 * kBoxBytes + off);
+            const float4 d4 = lds128(st + 2 * kBoxBytes + off);
+            const float4 w4 = lds128(st + 3 * kBoxBytes + off);
+            if (col0 + 4 < horizon) {   // column col0+3 is H-1 in the last unit of a row: no step
+                a_run = adv_step(v4.w, w4.w, nv, nr, nd, a_run, gamma, gl, rho_clip, c_clip);
+                out[4 * q + 3] = a_run;
+            }
+            a_run = adv_step(v4.z, w4.z, v4.w, r4.w, d4.w, a_run, gamma, gl, rho_clip, c_clip);
+            out[4 * q + 2] = a_run;
+            a_run = adv_step(v4.y, w4.y, v4.z, r4.z, d4.z, a_run, gamma, gl, rho_clip, c_clip);
+            out[4 * q + 1] = a_run;
+            a_run = adv_step(v4.x, w4.x, v4.y, r4.y, d4.y, a_run, gamma, gl, rho_clip, c_clip);
+            out[4 * q] = a_run;
+            nv = v4.x;
+            nr = r4.x;
+            nd = d4.x;
+        }
+    }
+}
+
+// Packed path for a chunk whose 32 columns all lie inside the row.  Everything
+// that does not depend on the running advantage is computed first, two steps
+// per instruction with the f32x2 forms of the same IEEE operations (so every
+// intermediate equals the scalar one bit for bit):
+//     nn = 1 - d'          as fma(d', -1, 1)       (the product is exact)
+//     delta = rho * ((r' + (gamma*v')*nn) - v),    k = ((gamma*lambda)*c) * nn
+// and the serial part is A = delta + k*A.  The reference evaluates
+// ((gamma*lambda*c)*A)*nn; for nn in {0, 1} that is the same fp32 value as
+// (gamma*lambda*c*nn)*A unless the inner product overflows.  Returns false --
+// and the caller redoes the chunk literally -- when any lane saw d'*nn != 0
+// (nn is not exactly 0 or 1) or advantages beyond 1e30.
+// `row_end`: column cbase+31 is H-1, which has no step.
+__device__ __forceinline__ bool chunk_packed(uint32_t st, uint32_t row_off, uint32_t sw, bool row_end,
+                                             float gamma, float gl, float rho_clip, float c_clip,
+                                             float& a_run, float& nv, float& nr, float& nd, float (&out)[32])
+{
+    float vc[33], rc[33], dc[33], wc[32];   // index j <-> column cbase + j; 32 = carried from the later chunk
+    vc[32] = nv;
+    rc[32] = nr;
+    dc[32] = nd;
+#pragma unroll
+    for (int u = 7; u >= 0; --u) {
+        const uint32_t off = row_off + ((static_cast<uint32_t>(u) ^ sw) << 4);
+        const float4 v4 = lds128(st + 0 * kBoxBytes + off);
+        const float4 r4 = lds128(st + 1 * kBoxBytes + off);
+        const float4 d4 = lds128(st + 2 * kBoxBytes + off);
+        const float4 w4 = lds128(st + 3 * kBoxBytes + off);
+        vc[4 * u] = v4.x; vc[4 * u + 1] = v4.y; vc[4 * u + 2] = v4.z; vc[4 * u + 3] = v4.w;
+        rc[4 * u] = r4.x; rc[4 * u + 1] = r4.y; rc[4 * u + 2] = r4.z; rc[4 * u + 3] = r4.w;
+        dc[4 * u] = d4.x; dc[4 * u + 1] = d4.y; dc[4 * u + 2] = d4.z; dc[4 * u + 3] = d4.w;
+        wc[4 * u] = w4.x; wc[4 * u + 1] = w4.y; wc[4 * u + 2] = w4.z; wc[4 * u + 3] = w4.w;
+    }
+    nv = vc[0];
+    nr = rc[0];
+    nd = dc[0];
+
+    float dl[32], kk[32];
+    uint32_t nonbin = 0u;
+    const float a_in = a_run;
+    // step 31 alone (its t+1 operands are the carried ones); masked at the end of a row
+    {
+        float d, g, n;
+        adv_terms(vc[31], wc[31], vc[32], rc[32], dc[32], gamma, gl, rho_clip, c_clip, d, g, n);
+        nonbin |= __float_as_uint(__fmul_rn(dc[32], n));
+        dl[31] = row_end ? 0.0f : d;
+        kk[31] = row_end ? 0.0f : __fmul_rn(g, n);
+    }
+    // steps (j, j+1) for odd j: their t+1 operands (j+1, j+2) are aligned register pairs
+    const float2 neg1 = make_float2(-1.0f, -1.0f), one2 = make_float2(1.0f, 1.0f);
+    const float2 gamma2 = make_float2(gamma, gamma), gl2 = make_float2(gl, gl);
+#pragma unroll
+    for (int j = 29; j >= 1; j -= 2) {
+        const float2 dn = make_float2(dc[j + 1], dc[j + 2]);
+        const float2 vn = make_float2(vc[j + 1], vc[j + 2]);
+        const float2 rn = make_float2(rc[j + 1], rc[j + 2]);
+        const float2 nn2 = __ffma2_rn(dn, neg1, one2);
+        const float2 t2 = __fadd2_rn(rn, __fmul2_rn(__fmul2_rn(gamma2, vn), nn2));
+        const float2 td2 = make_float2(__fsub_rn(t2.x, vc[j]), __fsub_rn(t2.y, vc[j + 1]));
+        const float2 rho2 = make_float2(fminf(wc[j], rho_clip), fminf(wc[j + 1], rho_clip));
+        const float2 c2 = make_float2(fminf(wc[j], c_clip), fminf(wc[j + 1], c_clip));
+        const float2 d2 = __fmul2_rn(rho2, td2);
+        const float2 k2 = __fmul2_rn(__fmul2_rn(gl2, c2), nn2);
+        const float2 q2 = __fmul2_rn(dn, nn2);
+        nonbin |= __float_as_uint(q2.x) | __float_as_uint(q2.y);
+        dl[j] = d2.x;
+        dl[j + 1] = d2.y;
+        kk[j] = k2.x;
+        kk[j + 1] = k2.y;
+    }
+    {
+        float d, g, n;
+        adv_terms(vc[0], wc[0], vc[1], rc[1], dc[1], gamma, gl, rho_clip, c_clip, d, g, n);
+        nonbin |= __float_as_uint(__fmul_rn(dc[1], n));
+        dl[0] = d;
+        kk[0] = __fmul_rn(g, n);
+    }
+    // the serial part
+    float a = a_in;
+#pragma unroll
+    for (int j = 31; j >= 0; --j) {
+        a = __fadd_rn(dl[j], __fmul_rn(kk[j], a));
+        out[j] = a;
+    }
+    a_run = a;
+    const float big = __fadd_rn(fabsf(a_in), abs_tree32(out));
+    const bool ok = ((nonbin << 1) == 0u) && (big <= 1e30f);
+    return __all_sync(0xffffffffu, ok);
 }
 
 // ---------------------------------------------------------------------------
@@ -292,39 +447,30 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
         const uint32_t st = base + s * kStageBytes;
         const uint32_t ob = out_base + (i & 1) * kBoxBytes;
         const int cbase = c * kChunkCols;
+        float out[32];   // advantages of columns cbase .. cbase+31 of this lane's row
+        const float a_in = a_run, nv_in = nv, nr_in = nr, nd_in = nd;
+        // Full chunks take the packed path; a last chunk that ends inside the box
+        // (H % 32 != 0) and chunks that fail the checks below take the literal one.
+        bool literal = (cbase + kChunkCols > horizon);
+        if (!literal) {
+            literal = !chunk_packed(st, row_off, sw, cbase + kChunkCols == horizon, gamma, gl, rho_clip, c_clip,
+                                    a_run, nv, nr, nd, out);
+        }
+        if (literal) {
+            a_run = a_in;
+            nv = nv_in;
+            nr = nr_in;
+            nd = nd_in;
+            chunk_literal(st, row_off, sw, cbase, horizon, gamma, gl, rho_clip, c_clip, a_run, nv, nr, nd, out);
+        }
+        if (EPI) abs_run = __fadd_rn(abs_run, abs_tree32(out));
 #pragma unroll
-        for (int q = 7; q >= 0; --q) {
-            const int col0 = cbase + 4 * q;
-            if (col0 < horizon) {   // warp-uniform
-                const uint32_t off = row_off + ((static_cast<uint32_t>(q) ^ sw) << 4);
-                const float4 v4 = lds128(st + 0 * kBoxBytes + off);
-                const float4 r4 = lds128(st + 1 * kBoxBytes + off);
-                const float4 d4 = lds128(st + 2 * kBoxBytes + off);
-                const float4 w4 = lds128(st + 3 * kBoxBytes + off);
-                float4 a4;
-                // column col0+3 is H-1 in the last unit of a row: no step there,
-                // the caller's value goes back unchanged
-                if (col0 + 4 < horizon) {
-                    a_run = adv_step(v4.w, w4.w, nv, nr, nd, a_run, gamma, gl, rho_clip, c_clip);
-                    if (EPI) abs_run = __fadd_rn(abs_run, fabsf(a_run));
-                    a4.w = a_run;
-                } else {
-                    a4.w = keep_last;
-                }
-                a_run = adv_step(v4.z, w4.z, v4.w, r4.w, d4.w, a_run, gamma, gl, rho_clip, c_clip);
-                if (EPI) abs_run = __fadd_rn(abs_run, fabsf(a_run));
-                a4.z = a_run;
-                a_run = adv_step(v4.y, w4.y, v4.z, r4.z, d4.z, a_run, gamma, gl, rho_clip, c_clip);
-                if (EPI) abs_run = __fadd_rn(abs_run, fabsf(a_run));
-                a4.y = a_run;
-                a_run = adv_step(v4.x, w4.x, v4.y, r4.y, d4.y, a_run, gamma, gl, rho_clip, c_clip);
-                if (EPI) abs_run = __fadd_rn(abs_run, fabsf(a_run));
-                a4.x = a_run;
-                nv = v4.x;
-                nr = r4.x;
-                nd = d4.x;
-                sts128(ob + off, a4);
-            }
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t off = row_off + ((static_cast<uint32_t>(u) ^ sw) << 4);
+            float4 a4 = make_float4(out[4 * u], out[4 * u + 1], out[4 * u + 2], out[4 * u + 3]);
+            // column H-1 (last of its unit, H % 4 == 0) goes back unchanged
+            if (cbase + 4 * u + 3 == horizon - 1) a4.w = keep_last;
+            sts128(ob + off, a4);
         }
         const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
         if (EPI && c == 0) {
@@ -716,6 +862,13 @@ struct DeviceInfo {
 static DeviceInfo g_dev[64];
 static std::mutex g_dev_mutex;
 
+template <int NST>
+static void set_tma2d_attrs()
+{
+    cudaFuncSetAttribute(puff_adv_tma2d_kernel<NST, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<NST>());
+    cudaFuncSetAttribute(puff_adv_tma2d_kernel<NST, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<NST>());
+}
+
 static const DeviceInfo* device_info(int* code)
 {
     int dev = 0;
@@ -738,12 +891,12 @@ static const DeviceInfo* device_info(int* code)
             d.err = e1 != cudaSuccess ? e1 : (e2 != cudaSuccess ? e2 : e3);
             if (d.err == cudaSuccess) {
                 // opt in to large dynamic shared memory once per device
-                cudaFuncSetAttribute(puff_adv_tma2d_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<2>());
-                cudaFuncSetAttribute(puff_adv_tma2d_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<2>());
-                cudaFuncSetAttribute(puff_adv_tma2d_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<3>());
-                cudaFuncSetAttribute(puff_adv_tma2d_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<3>());
-                cudaFuncSetAttribute(puff_adv_tma2d_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<4>());
-                cudaFuncSetAttribute(puff_adv_tma2d_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<4>());
+                set_tma2d_attrs<2>();
+                set_tma2d_attrs<3>();
+                set_tma2d_attrs<4>();
+                set_tma2d_attrs<6>();
+                set_tma2d_attrs<8>();
+                set_tma2d_attrs<12>();
                 cudaFuncSetAttribute(puff_adv_bulk1d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem_optin);
                 d.err = cudaGetLastError();
             }
@@ -935,8 +1088,17 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
         // TMA coordinates are 32-bit: process blocks of at most 2^30 rows
         const long long block_rows = 1LL << 30;
         static thread_local MapSet cache;
-        const int nst = env_int("PUFF_ADV_STAGES", 3);
-        const int ctas_per_sm = nst <= 2 ? 5 : 3;
+        // measured on cfg2 (131072 x 256): two CTAs per SM with a four-stage ring each
+        // beat both more, shallower CTAs and one deeper CTA
+        int nst = env_int("PUFF_ADV_STAGES", 4);
+        nst = nst <= 2 ? 2 : nst == 3 ? 3 : nst == 4 ? 4 : nst <= 6 ? 6 : nst <= 8 ? 8 : 12;
+        const int stage_smem = nst * kStageBytes + 2 * kBoxBytes + nst * 8 + 1024;
+        int ctas_per_sm = (dev->max_smem_optin + 1024) / (stage_smem + 1024);
+        {
+            const int o = env_int("PUFF_ADV_CTAS_PER_SM", nst == 4 ? 2 : 0);
+            if (o > 0 && o < ctas_per_sm) ctas_per_sm = o;
+        }
+        if (ctas_per_sm < 1) ctas_per_sm = 1;
         for (long long r0 = 0; r0 < num_segments && err == cudaSuccess; r0 += block_rows) {
             const long long rows = num_segments - r0 < block_rows ? num_segments - r0 : block_rows;
             const long long off = r0 * horizon;
@@ -955,12 +1117,18 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
             const long long max_grid = static_cast<long long>(dev->sm_count) * ctas_per_sm;
             const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
             float* abs_p = seg_abs_sum != nullptr ? seg_abs_sum + r0 : nullptr;
-            if (nst <= 2)
-                err = launch_tma2d<2>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st);
-            else if (nst == 3)
-                err = launch_tma2d<3>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st);
-            else
-                err = launch_tma2d<4>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st);
+#define PUFF_TMA2D_CASE(N)                                                                               \
+    err = launch_tma2d<N>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, \
+                          static_cast<int>(tiles), st)
+            switch (nst) {
+                case 2: PUFF_TMA2D_CASE(2); break;
+                case 3: PUFF_TMA2D_CASE(3); break;
+                case 4: PUFF_TMA2D_CASE(4); break;
+                case 6: PUFF_TMA2D_CASE(6); break;
+                case 8: PUFF_TMA2D_CASE(8); break;
+                default: PUFF_TMA2D_CASE(12); break;
+            }
+#undef PUFF_TMA2D_CASE
             g_launch_count.fetch_add(1, std::memory_order_relaxed);
         }
     } else if (kernel == PUFF_KERNEL_BULK1D) {

@@ -267,3 +267,37 @@ def test_hyperparameter_edges():
     for variant in ("serial", "scan"):
         got, _, _ = run_gpu(ones, wl.hyper(), variant)
         assert bits_equal(got, want)   # all episodes end every step: no carry, so scan is exact too
+
+
+def test_products_near_overflow_follow_the_reference_order():
+    """(gamma*lambda*c*A)*nn turns into NaN in the reference when the inner
+    product overflows and nn == 0; the kernels must reproduce that, not the
+    re-associated (gamma*lambda*c*nn)*A == 0."""
+    S, H = 40, 64
+    rng = np.random.default_rng(5)
+    v = rng.standard_normal((S, H)).astype(np.float32)
+    r = rng.standard_normal((S, H)).astype(np.float32)
+    d = (rng.random((S, H)) < 0.2).astype(np.float32)
+    w = np.full((S, H), 4.0, dtype=np.float32)
+    r[:, 40] = 2.5e38          # the advantage at column 39 becomes ~1e38 * rho
+    d[:, 39] = 1.0             # and the step at column 38 multiplies its overflowed product by nn = 0
+    d[:, 40] = 0.0
+    hyper = (1.0, 1.0, 1.0, 4.0)
+    want = oracle_advantage([v, r, d, w], hyper)
+    assert np.isnan(want[:, 38]).all()
+    for force in ("tma2d", "bulk1d", "generic"):
+        got, _, _ = run_gpu([v, r, d, w], hyper, "serial", force)
+        assert bits_equal(got, want), (force, first_mismatch(got, want))
+
+
+def test_non_binary_dones_are_used_arithmetically():
+    """dones enter as 1 - d (pufferlib.cpp:34), not as a branch: fractional
+    values must give the reference's bits on every serial kernel."""
+    wl = Workload("frac", 70, 128, seed=91)
+    v, r, d, w = [t.numpy() for t in make_inputs(wl)]
+    d = np.random.default_rng(3).random(d.shape).astype(np.float32)
+    d[::3] = (d[::3] > 0.5)          # a mix of binary and fractional rows inside every tile
+    want = oracle_advantage([v, r, d, w], wl.hyper())
+    for force in ("tma2d", "bulk1d", "generic"):
+        got, _, _ = run_gpu([v, r, d, w], wl.hyper(), "serial", force)
+        assert bits_equal(got, want), (force, first_mismatch(got, want))
