@@ -152,3 +152,22 @@ def test_priorities_non_finite_sums_become_zero_weight():
     w, tot = pufferlib_b200.priority_weights(s, 0.5)
     assert w.cpu().tolist() == pytest.approx([1.0, 0.0, 0.0, 0.0, 2.0 ** 0.5], rel=1e-6)
     assert float(tot) == pytest.approx(1.0 + 2.0 ** 0.5, rel=1e-6)
+
+
+def test_standalone_nvcc_harness(tmp_path):
+    """A torch-free nvcc program drives the C ABI (the reference's harness style)."""
+    import os
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    libdir = os.path.join(root, "pufferlib_b200")
+    exe = str(tmp_path / "harness")
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-o", exe,
+                    os.path.join(root, "tests", "harness_puff_advantage.cu"),
+                    f"-L{libdir}", "-lpuff_advantage_sm100", "-Xlinker", f"-rpath={libdir}"], check=True)
+    out = subprocess.run([exe], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "OK" in out.stdout
