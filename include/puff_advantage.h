@@ -121,6 +121,39 @@ int puff_priorities_sm100_probs(const float* weights, const double* total_w,
                                 float* probs, long long num_segments,
                                 void* cuda_stream);
 
+/*
+ * puff_priorities_sm100_weights for callers that cannot supply scratch.
+ * (No counterpart in the reference, which allocates freely through torch.)
+ *
+ * Some hosts of this library have no way to allocate device memory at the
+ * point of the call: a C or FFI caller inside a trainer whose GPU memory is
+ * already fully owned by the policy, the experience buffers and the
+ * framework's caching allocator, or a wrapper that holds no allocator handle
+ * at all.  There cudaMalloc can fail, and even when it works it stalls the
+ * device between minibatches.  This variant takes the same inputs and outputs
+ * as puff_priorities_sm100_weights but keeps its partial sums in a fixed array
+ * inside the library image (4 KB per GPU that loads the library, held until
+ * the process exits), and calls no allocation routine of CUDA or any other
+ * library.
+ *
+ * Limits and rules:
+ *  - num_segments <= PUFF_NOALLOC_MAX_SEGMENTS, otherwise PUFF_ERR_SIZE and
+ *    nothing is launched.
+ *  - The first call on each device looks up the array's device address (that
+ *    device must be current, as for every launch here).  Make that first call
+ *    during set-up, before any stream capture is started.
+ *  - All calls on a device share the one array.  Calls are safe back to back
+ *    on one stream; two calls that can overlap on the GPU (different streams
+ *    without an ordering between them) race on it and must be serialised by
+ *    the caller.  Nothing needs clearing between calls: each call overwrites
+ *    every entry it later reads.
+ * Results are identical to puff_priorities_sm100_weights.
+ */
+#define PUFF_NOALLOC_MAX_SEGMENTS 524288LL
+int puff_priorities_sm100_weights_noalloc(const float* seg_abs_sum, float* weights,
+                                          double* total_w, float alpha,
+                                          long long num_segments, void* cuda_stream);
+
 /* ---- introspection ------------------------------------------------------- */
 /* Human-readable text for a return code of any entry point above. */
 const char* puff_advantage_sm100_strerror(int code);

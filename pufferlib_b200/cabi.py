@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libpuff_advantage_sm100.so")
 OK = 0
 ERR_NULL, ERR_SHAPE, ERR_VARIANT, ERR_ALIGN, ERR_ALIAS = -1, -2, -3, -4, -5
 ERR_ARCH, ERR_DRIVER, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_SIZE = -6, -7, -8, -9, -10
+NOALLOC_MAX_SEGMENTS = 524288
 VARIANT_AUTO, VARIANT_SERIAL, VARIANT_SCAN, VARIANT_GENERIC = 0, 1, 2, 3
 KERNEL_NONE, KERNEL_TMA2D, KERNEL_BULK1D, KERNEL_SCAN, KERNEL_GENERIC = 0, 1, 2, 3, 4
 VARIANTS = {"auto": VARIANT_AUTO, "serial": VARIANT_SERIAL, "scan": VARIANT_SCAN, "generic": VARIANT_GENERIC}
@@ -35,6 +36,7 @@ SIGNATURES = {
     "puff_priorities_sm100_scratch_bytes": (ctypes.c_size_t, [_LL]),
     "puff_priorities_sm100_weights": (_I, [_P, _P, _P, _F, _LL, _P, ctypes.c_size_t, _P]),
     "puff_priorities_sm100_probs": (_I, [_P, _P, _P, _LL, _P]),
+    "puff_priorities_sm100_weights_noalloc": (_I, [_P, _P, _P, _F, _LL, _P]),
     "puff_advantage_sm100_strerror": (ctypes.c_char_p, [_I]),
     "puff_advantage_sm100_last_kernel": (_I, []),
     "puff_advantage_sm100_launch_count": (_LL, []),

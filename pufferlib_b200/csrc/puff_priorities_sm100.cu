@@ -12,6 +12,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/puff_advantage.h"
 
 namespace puff {
@@ -128,6 +130,81 @@ extern "C" int puff_priorities_sm100_probs(const float* weights, const double* t
     long long blocks = (num_segments + kPrioThreads - 1) / kPrioThreads;
     if (blocks > 148 * 8) blocks = 148 * 8;
     puff_prio_probs_kernel<<<static_cast<int>(blocks), kPrioThreads, 0, st>>>(weights, total_w, probs, num_segments);
+    count_launch();
+    return static_cast<int>(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------
+// priority weights without any allocation
+// ---------------------------------------------------------------------------
+// puff_priorities_sm100_weights needs a few KB of scratch for its per-CTA
+// partial sums and expects the caller to own it.  A caller that sits behind a
+// plain C FFI inside a trainer whose device memory is already carved up -- the
+// policy, the experience buffers and the framework's caching allocator hold
+// all of it, or the host wrapper simply has no allocator handle to pass down --
+// cannot produce that buffer: cudaMalloc there may fail outright, and where it
+// succeeds it stalls the device in the middle of the minibatch loop.  For such
+// callers the scratch lives in the library image instead: one fixed array per
+// GPU that loads this library, held until the process exits.
+//
+// The array is sized for kNoAllocMaxBlocks partial sums (4 KB), which covers
+// PUFF_NOALLOC_MAX_SEGMENTS segments; larger requests are refused, not
+// truncated.  `g_noalloc_partials` below is the device symbol; in host code
+// that name is only a stand-in, so the real device address is looked up with
+// cudaGetSymbolAddress once per device (with that device current) and that
+// pointer is what the kernels receive.
+constexpr int kNoAllocMaxBlocks = 512;
+static_assert(static_cast<long long>(kNoAllocMaxBlocks) * kPrioThreads * 4 == PUFF_NOALLOC_MAX_SEGMENTS,
+              "header limit and scratch size disagree");
+static __device__ __align__(256) double g_noalloc_partials[kNoAllocMaxBlocks];
+
+namespace puff {
+constexpr int kNoAllocMaxDevices = 64;
+static std::mutex g_noalloc_mutex;
+static double* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+
+// Device address of the scratch array on the current device; looked up on the
+// first call per device and cached.
+static int noalloc_scratch(double** out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return PUFF_ERR_ARCH;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_partials);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        if (p == nullptr) return PUFF_ERR_WORKSPACE;
+        g_noalloc_ptr[dev] = static_cast<double*>(p);
+    }
+    *out = g_noalloc_ptr[dev];
+    return PUFF_OK;
+}
+}  // namespace puff
+
+extern "C" int puff_priorities_sm100_weights_noalloc(const float* seg_abs_sum, float* weights, double* total_w,
+                                                     float alpha, long long num_segments, void* cuda_stream)
+{
+    if (num_segments < 0) return PUFF_ERR_SHAPE;
+    if (num_segments > PUFF_NOALLOC_MAX_SEGMENTS) return PUFF_ERR_SIZE;
+    if (total_w == nullptr) return PUFF_ERR_NULL;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    if (num_segments == 0) return static_cast<int>(cudaMemsetAsync(total_w, 0, sizeof(double), st));
+    if (seg_abs_sum == nullptr || weights == nullptr) return PUFF_ERR_NULL;
+    double* partial = nullptr;
+    const int rc = noalloc_scratch(&partial);
+    if (rc != PUFF_OK) return rc;
+    // Nothing in the scratch has to start at zero: the first kernel overwrites
+    // partial[0 .. blocks) and the second reads exactly those entries, so
+    // whatever an earlier (possibly larger) call left behind is never read.
+    const int blocks = prio_blocks(num_segments);
+    puff_prio_weights_kernel<<<blocks, kPrioThreads, 0, st>>>(seg_abs_sum, weights, partial, alpha, num_segments);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    puff_prio_total_kernel<<<1, kPrioThreads, 0, st>>>(partial, blocks, total_w);
     count_launch();
     return static_cast<int>(cudaGetLastError());
 }
