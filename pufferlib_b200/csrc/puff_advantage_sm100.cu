@@ -501,18 +501,367 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// tma2d, warp-specialised: one CTA per tile stream, six warps with three roles
+// ---------------------------------------------------------------------------
+// A lone warp per tile cannot issue instructions fast enough to keep up with
+// HBM once the pipeline is deep (measured: one such warp per SM is compute
+// bound at about a third of the bandwidth).  Here the work of a 32x32 chunk is
+// split by dependency instead:
+//   warp 0      producer: waits for a free stage, issues the four TMA loads
+//   warps 2..5  terms:    128 threads, 8 columns of one row each, read the raw
+//                         boxes and write (delta, gamma*lambda*c, nn) for every
+//                         step into a terms buffer (same swizzled layout);
+//                         columns without a step get delta = gc = 0
+//   warp 1      chain:    lane r walks row r's 32 steps from the terms buffer,
+//                         A = delta + (gc*nn)*A (or the literal order when the
+//                         terms warps flagged a non-binary nn or A nears the
+//                         overflow range), stores the advantages by TMA
+// Rings: NST raw stages (full: TMA -> terms, sfree: terms -> producer) and NT
+// terms buffers (tfull: terms -> chain, tfree: chain -> terms).
+constexpr int kWsTermWarps = 4;
+constexpr int kWsThreads = 32 * (2 + kWsTermWarps);
+constexpr int kTermBytes = 4 * kBoxBytes;   // delta | k = gc*nn | gc | nn
+
+constexpr int kWsOutSlots = 4;   // output boxes in flight behind the TMA stores
+template <int NST, int NT>
+constexpr int tma2d_ws_smem_bytes()
+{
+    return NST * kStageBytes + NT * kTermBytes + kWsOutSlots * kBoxBytes + (2 * NST + 2 * NT) * 8 + NT * 4 + 64 + 1024;
+}
+
+__device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok = mbar_try_wait(bar, parity);
+    if (!ok) {
+        const unsigned long long t0 = global_ns();
+        uint32_t polls = 0;
+        while (!ok && polls < kWaitLimit) {
+            ok = mbar_try_wait(bar, parity);
+            if ((++polls & 1023u) == 0u && global_ns() - t0 > kWaitLimitNs) break;
+        }
+    }
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ float lds32(uint32_t addr)
+{
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32u(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts32u(uint32_t addr, uint32_t v)
+{
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+template <int NST, int NT, bool EPI>
+__global__ void __launch_bounds__(kWsThreads)
+puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
+                         const __grid_constant__ CUtensorMap tm_r,
+                         const __grid_constant__ CUtensorMap tm_d,
+                         const __grid_constant__ CUtensorMap tm_w,
+                         const __grid_constant__ CUtensorMap tm_a,
+                         const float* adv_in, float* __restrict__ seg_abs_sum, float gamma, float lambda,
+                         float rho_clip, float c_clip, long long num_segments, int horizon, int num_tiles)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t term_base = base + NST * kStageBytes;
+    const uint32_t out_base = term_base + NT * kTermBytes;
+    const uint32_t bar_full = out_base + kWsOutSlots * kBoxBytes;
+    const uint32_t bar_sfree = bar_full + 8 * NST;
+    const uint32_t bar_tfull = bar_sfree + 8 * NST;
+    const uint32_t bar_tfree = bar_tfull + 8 * NT;
+    const uint32_t flag_base = bar_tfree + 8 * NT;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                         static_cast<int>(gridDim.x);
+    const int nchunks = (horizon + kChunkCols - 1) / kChunkCols;
+    const int total = my_tiles * nchunks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_sfree + 8 * s, kWsTermWarps);
+        }
+        for (int b = 0; b < NT; ++b) {
+            mbar_init(bar_tfull + 8 * b, kWsTermWarps);
+            mbar_init(bar_tfree + 8 * b, 1);
+            sts32u(flag_base + 4 * b, 0u);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    const float gl = __fmul_rn(gamma, lambda);
+    bool failed = false;
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            prefetch_tensormap(&tm_v);
+            prefetch_tensormap(&tm_r);
+            prefetch_tensormap(&tm_d);
+            prefetch_tensormap(&tm_w);
+            int k = 0, c = nchunks - 1, s = 0, round = 0;
+            for (int i = 0; i < total; ++i) {
+                if (round > 0 && !mbar_wait_thread(bar_sfree + 8 * s, static_cast<uint32_t>(round - 1) & 1u)) {
+                    failed = true;
+                    break;
+                }
+                const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+                const uint32_t st = base + s * kStageBytes;
+                const uint32_t bar = bar_full + 8 * s;
+                const int x = c * kChunkCols, y = tile * kTileRows;
+                mbar_expect_tx(bar, kStageBytes);
+                tma_load_2d(st + 0 * kBoxBytes, &tm_v, x, y, bar);
+                tma_load_2d(st + 1 * kBoxBytes, &tm_r, x, y, bar);
+                tma_load_2d(st + 2 * kBoxBytes, &tm_d, x, y, bar);
+                tma_load_2d(st + 3 * kBoxBytes, &tm_w, x, y, bar);
+                if (--c < 0) {
+                    c = nchunks - 1;
+                    ++k;
+                }
+                if (++s == NST) {
+                    s = 0;
+                    ++round;
+                }
+            }
+            if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+        }
+    } else if (warp >= 2) {
+        // ------------------------------- terms --------------------------------
+        const int tt = (warp - 2) * 32 + lane;   // 0..127
+        const int row = tt >> 2;                  // row of the tile
+        const int g = tt & 3;                     // which 8 columns of the chunk
+        const uint32_t rsw = static_cast<uint32_t>(row) & 7u;
+        const uint32_t off0 = static_cast<uint32_t>(row) * 128u + (((2u * g) ^ rsw) << 4);
+        const uint32_t off1 = static_cast<uint32_t>(row) * 128u + (((2u * g + 1u) ^ rsw) << 4);
+        const uint32_t offn = static_cast<uint32_t>(row) * 128u + ((((2u * g + 2u) & 7u) ^ rsw) << 4);
+        float first_v = 0.0f, first_r = 0.0f, first_d = 0.0f;   // column 0 of the previous (later) chunk
+        int c = nchunks - 1, s = 0, b = 0;
+        uint32_t sround = 0, bround = 0;
+        for (int i = 0; i < total; ++i) {
+            if (c == nchunks - 1) {   // tile start: nothing carries over
+                first_v = 0.0f;
+                first_r = 0.0f;
+                first_d = 0.0f;
+            }
+            if (!mbar_wait_warp(bar_full + 8 * s, sround & 1u)) {
+                failed = true;
+                break;
+            }
+            if (bround > 0 && !mbar_wait_warp(bar_tfree + 8 * b, (bround - 1) & 1u)) {
+                failed = true;
+                break;
+            }
+            const uint32_t st = base + s * kStageBytes;
+            float v[9], r[9], d[9], w[8];
+            {
+                const float4 a0 = lds128(st + 0 * kBoxBytes + off0), a1 = lds128(st + 0 * kBoxBytes + off1);
+                v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+                const float4 b0 = lds128(st + 1 * kBoxBytes + off0), b1 = lds128(st + 1 * kBoxBytes + off1);
+                r[0] = b0.x; r[1] = b0.y; r[2] = b0.z; r[3] = b0.w; r[4] = b1.x; r[5] = b1.y; r[6] = b1.z; r[7] = b1.w;
+                const float4 c0 = lds128(st + 2 * kBoxBytes + off0), c1 = lds128(st + 2 * kBoxBytes + off1);
+                d[0] = c0.x; d[1] = c0.y; d[2] = c0.z; d[3] = c0.w; d[4] = c1.x; d[5] = c1.y; d[6] = c1.z; d[7] = c1.w;
+                const float4 e0 = lds128(st + 3 * kBoxBytes + off0), e1 = lds128(st + 3 * kBoxBytes + off1);
+                w[0] = e0.x; w[1] = e0.y; w[2] = e0.z; w[3] = e0.w; w[4] = e1.x; w[5] = e1.y; w[6] = e1.z; w[7] = e1.w;
+            }
+            // column 8g+8: the next unit of the same row, or (g == 3) the carried column
+            const float nv_s = lds32(st + 0 * kBoxBytes + offn);
+            const float nr_s = lds32(st + 1 * kBoxBytes + offn);
+            const float nd_s = lds32(st + 2 * kBoxBytes + offn);
+            const float nv_c = __shfl_sync(0xffffffffu, first_v, (lane & ~3));
+            const float nr_c = __shfl_sync(0xffffffffu, first_r, (lane & ~3));
+            const float nd_c = __shfl_sync(0xffffffffu, first_d, (lane & ~3));
+            v[8] = g == 3 ? nv_c : nv_s;
+            r[8] = g == 3 ? nr_c : nr_s;
+            d[8] = g == 3 ? nd_c : nd_s;
+            first_v = v[0];
+            first_r = r[0];
+            first_d = d[0];
+            const int col0 = c * kChunkCols + 8 * g;
+            float dl[8], kk[8], gc[8], nn[8];
+            uint32_t nonbin = 0u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool valid = col0 + j < horizon - 1;
+                adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dl[j], gc[j], nn[j]);
+                dl[j] = valid ? dl[j] : 0.0f;
+                gc[j] = valid ? gc[j] : 0.0f;
+                kk[j] = __fmul_rn(gc[j], nn[j]);
+                nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nn[j])) : 0u;
+            }
+            const uint32_t tb = term_base + b * kTermBytes;
+            sts128(tb + 0 * kBoxBytes + off0, make_float4(dl[0], dl[1], dl[2], dl[3]));
+            sts128(tb + 0 * kBoxBytes + off1, make_float4(dl[4], dl[5], dl[6], dl[7]));
+            sts128(tb + 1 * kBoxBytes + off0, make_float4(kk[0], kk[1], kk[2], kk[3]));
+            sts128(tb + 1 * kBoxBytes + off1, make_float4(kk[4], kk[5], kk[6], kk[7]));
+            sts128(tb + 2 * kBoxBytes + off0, make_float4(gc[0], gc[1], gc[2], gc[3]));
+            sts128(tb + 2 * kBoxBytes + off1, make_float4(gc[4], gc[5], gc[6], gc[7]));
+            sts128(tb + 3 * kBoxBytes + off0, make_float4(nn[0], nn[1], nn[2], nn[3]));
+            sts128(tb + 3 * kBoxBytes + off1, make_float4(nn[4], nn[5], nn[6], nn[7]));
+            if ((nonbin << 1) != 0u) sts32u(flag_base + 4 * b, 1u);
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_tfull + 8 * b);
+                mbar_arrive(bar_sfree + 8 * s);
+            }
+            if (--c < 0) c = nchunks - 1;
+            if (++s == NST) {
+                s = 0;
+                ++sround;
+            }
+            if (++b == NT) {
+                b = 0;
+                ++bround;
+            }
+        }
+        if (failed && lane == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+    } else {
+        // ------------------------------- chain --------------------------------
+        if (lane == 0) prefetch_tensormap(&tm_a);
+        const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
+        const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
+        float a_run = 0.0f, abs_run = 0.0f, keep_last = 0.0f;
+        int k = 0, c = nchunks - 1, b = 0, oslot = 0;
+        uint32_t bround = 0;
+        for (int i = 0; i < total; ++i) {
+            const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+            if (c == nchunks - 1) {   // tile start
+                const long long row = static_cast<long long>(tile) * kTileRows + lane;
+                keep_last = row < num_segments ? adv_in[row * horizon + horizon - 1] : 0.0f;
+                a_run = 0.0f;
+                abs_run = 0.0f;
+            }
+            if (!mbar_wait_warp(bar_tfull + 8 * b, bround & 1u)) {
+                failed = true;
+                break;
+            }
+            const uint32_t tb = term_base + b * kTermBytes;
+            float dl[32], kk[32], out[32];
+#pragma unroll
+            for (int u = 7; u >= 0; --u) {
+                const uint32_t off = row_off + ((static_cast<uint32_t>(u) ^ sw) << 4);
+                const float4 x = lds128(tb + 0 * kBoxBytes + off);
+                const float4 y = lds128(tb + 1 * kBoxBytes + off);
+                dl[4 * u] = x.x; dl[4 * u + 1] = x.y; dl[4 * u + 2] = x.z; dl[4 * u + 3] = x.w;
+                kk[4 * u] = y.x; kk[4 * u + 1] = y.y; kk[4 * u + 2] = y.z; kk[4 * u + 3] = y.w;
+            }
+            const uint32_t flag = lds32u(flag_base + 4 * b);
+            const float a_in = a_run;
+            bool literal = flag != 0u;
+            float abs_chunk = 0.0f;
+            if (!literal) {
+#pragma unroll
+                for (int j = 31; j >= 0; --j) {
+                    a_run = __fadd_rn(dl[j], __fmul_rn(kk[j], a_run));
+                    out[j] = a_run;
+                }
+                abs_chunk = abs_tree32(out);
+                literal = __any_sync(0xffffffffu, !(__fadd_rn(fabsf(a_in), abs_chunk) <= 1e30f));
+            }
+            if (literal) {   // rare: the reference's literal order, from gc and nn
+                a_run = a_in;
+#pragma unroll
+                for (int u = 7; u >= 0; --u) {
+                    const uint32_t off = row_off + ((static_cast<uint32_t>(u) ^ sw) << 4);
+                    const float4 y = lds128(tb + 2 * kBoxBytes + off);
+                    const float4 z = lds128(tb + 3 * kBoxBytes + off);
+                    a_run = __fadd_rn(dl[4 * u + 3], __fmul_rn(__fmul_rn(y.w, a_run), z.w));
+                    out[4 * u + 3] = a_run;
+                    a_run = __fadd_rn(dl[4 * u + 2], __fmul_rn(__fmul_rn(y.z, a_run), z.z));
+                    out[4 * u + 2] = a_run;
+                    a_run = __fadd_rn(dl[4 * u + 1], __fmul_rn(__fmul_rn(y.y, a_run), z.y));
+                    out[4 * u + 1] = a_run;
+                    a_run = __fadd_rn(dl[4 * u], __fmul_rn(__fmul_rn(y.x, a_run), z.x));
+                    out[4 * u] = a_run;
+                }
+                abs_chunk = abs_tree32(out);
+            }
+            // the terms buffer is free once every lane has its values (and the rare path is done)
+            __syncwarp();
+            if (lane == 0) {
+                if (flag != 0u) sts32u(flag_base + 4 * b, 0u);
+                mbar_arrive(bar_tfree + 8 * b);
+            }
+            if (EPI) abs_run = __fadd_rn(abs_run, abs_chunk);
+            const uint32_t ob = out_base + oslot * kBoxBytes;
+            const int cbase = c * kChunkCols;
+            if (lane == 0) bulk_wait_read<kWsOutSlots - 1>();   // the store that last used this box has read it
+            __syncwarp();
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t off = row_off + ((static_cast<uint32_t>(u) ^ sw) << 4);
+                float4 a4 = make_float4(out[4 * u], out[4 * u + 1], out[4 * u + 2], out[4 * u + 3]);
+                if (cbase + 4 * u + 3 == horizon - 1) a4.w = keep_last;
+                sts128(ob + off, a4);
+            }
+            if (EPI && c == 0) {
+                const long long row = static_cast<long long>(tile) * kTileRows + lane;
+                if (row < num_segments) seg_abs_sum[row] = abs_run;
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(&tm_a, cbase, tile * kTileRows, ob);
+                bulk_commit();
+            }
+            if (--c < 0) {
+                c = nchunks - 1;
+                ++k;
+            }
+            if (++b == NT) {
+                b = 0;
+                ++bround;
+            }
+            if (++oslot == kWsOutSlots) oslot = 0;
+        }
+        if (lane == 0) {
+            bulk_wait_all();
+            if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // bulk1d: serial, dense tiles of `tile_rows` whole rows fetched by 1-D bulk copies
 // ---------------------------------------------------------------------------
-// Shared memory: 2 stages x 4 arrays x tile_rows*H floats, then 2 mbarriers.
-// A tile is a contiguous span of tile_rows*H*4 bytes per array; tile_rows is a
-// multiple of 4, so every tile starts on a 16-byte boundary for any H.  The
-// last tile of the buffer may hold a row count whose byte size is not a
-// multiple of 16; it is fetched with plain loads instead.  Lane r < tile_rows
-// walks row r (stride H words: conflict-free for odd H), writes the advantages
-// over the consumed importance slot, and the warp then stores the tile with
-// coalesced stores that skip column H-1.
-__global__ void __launch_bounds__(32)
+// For H % 4 != 0 the row pitch is not a multiple of 16 bytes and no 2-D tensor
+// map exists, but a tile of whole rows is one contiguous span per array;
+// tile_rows is a multiple of 4, so every tile starts on a 16-byte boundary for
+// any H.  (The last tile of a buffer may have a byte size that is not a
+// multiple of 16: it is fetched with plain loads.)
+//
+// One CTA of four warps per tile, one stage of shared memory (v | r | d | w,
+// dense, pitch H); several CTAs per SM overlap each other's phases:
+//   1. thread 0 issues four cp.async.bulk copies, everybody waits on the mbarrier
+//   2. terms, all 128 threads over the flat tile: delta, k = gc*nn, gc, nn of
+//      every step, written in place (delta -> w, k -> r, gc -> d, nn -> v).  Element
+//      e is read only by the threads that own e and e-1, so a batch that reads
+//      all its operands, synchronises, then writes cannot clobber live inputs.
+//   3. chain, warp 0: lane r walks row r, A = delta + k*A, A written over k
+//      (stride H words: conflict-free for odd H); literal order from gc and nn
+//      when a non-binary nn was seen or A nears the overflow range
+//   4. copy-out, all threads: coalesced 128-bit stores that skip column H-1
+constexpr int kB1Threads = 128;
+constexpr int kB1Batch = 4;   // elements per thread between synchronisations
+
+__global__ void __launch_bounds__(kB1Threads)
 puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
                        const float* __restrict__ dones, const float* __restrict__ importance,
                        float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
@@ -522,123 +871,195 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     float* const smem_f = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
-    const int lane = threadIdx.x;
+    const int tid = threadIdx.x;
     const int tile_elems = tile_rows * horizon;
-    const uint32_t arr_bytes = static_cast<uint32_t>(tile_elems) * 4u;
-    const uint32_t arr_pitch = (arr_bytes + 15u) & ~15u;     // keep every array 16-byte aligned
-    const uint32_t stage_bytes = 4u * arr_pitch;
-    const uint32_t bar_base = base + 2u * stage_bytes;
+    const uint32_t arr_pitch = (static_cast<uint32_t>(tile_elems) * 4u + 15u) & ~15u;   // bytes, 16-byte aligned
+    const uint32_t bar = base + 4u * arr_pitch;
+    float* const sv = smem_f;
+    float* const sr = sv + arr_pitch / 4;
+    float* const sd = sr + arr_pitch / 4;
+    float* const swt = sd + arr_pitch / 4;
 
-    if (static_cast<long long>(blockIdx.x) >= num_tiles) return;
-    const long long my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
-
-    if (lane == 0) {
-        mbar_init(bar_base, 1);
-        mbar_init(bar_base + 8, 1);
+    if (tid == 0) {
+        mbar_init(bar, 1);
         fence_mbar_init();
         fence_proxy_async();
     }
-    __syncwarp();
+    __syncthreads();
 
-    const float* const src[4] = {values, rewards, dones, importance};
-
-    // rows in tile, and whether the tile can come in by bulk copy
-    auto tile_rows_of = [&](long long tile) {
-        const long long rem = num_segments - tile * tile_rows;
-        return static_cast<int>(rem < tile_rows ? rem : tile_rows);
-    };
-    auto fetch = [&](long long n, int s) {   // whole warp calls this
-        const long long tile = blockIdx.x + n * gridDim.x;
-        const int rows = tile_rows_of(tile);
-        const uint32_t bytes = static_cast<uint32_t>(rows) * horizon * 4u;
-        const long long goff = tile * tile_elems;
-        const uint32_t st = base + s * stage_bytes;
-        if ((bytes & 15u) == 0u) {
-            if (lane == 0) {
-                mbar_expect_tx(bar_base + 8 * s, 4u * bytes);
-                for (int a = 0; a < 4; ++a) bulk_load_1d(st + a * arr_pitch, src[a] + goff, bytes, bar_base + 8 * s);
-            }
-        } else {
-            float* const dst = smem_f + (s * stage_bytes) / 4;
-            const int n_el = rows * horizon;
-            for (int a = 0; a < 4; ++a) {
-                const float* g = src[a] + goff;
-                float* d = dst + (a * arr_pitch) / 4;
-                for (int e = lane; e < n_el; e += 32) d[e] = __ldg(g + e);
-            }
-        }
-    };
-    auto bulk_tile = [&](long long n) {
-        const long long tile = blockIdx.x + n * gridDim.x;
-        return ((static_cast<uint32_t>(tile_rows_of(tile)) * horizon * 4u) & 15u) == 0u;
-    };
-
-    fetch(0, 0);
     const float gl = __fmul_rn(gamma, lambda);
-    uint32_t parity[2] = {0u, 0u};
+    const float* const src[4] = {values, rewards, dones, importance};
+    uint32_t parity = 0u;
     bool failed = false;
 
-    for (long long n = 0; n < my_tiles; ++n) {
-        const int s = static_cast<int>(n & 1);
-        if (n + 1 < my_tiles) fetch(n + 1, s ^ 1);
-        if (bulk_tile(n)) {
-            if (!mbar_wait_warp(bar_base + 8 * s, parity[s])) {
+    for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const long long rem = num_segments - tile * tile_rows;
+        const int rows = static_cast<int>(rem < tile_rows ? rem : tile_rows);
+        const int n_el = rows * horizon;
+        const uint32_t bytes = static_cast<uint32_t>(n_el) * 4u;
+        const long long goff = tile * tile_elems;
+        // ---- 1. fetch ----
+        if ((bytes & 15u) == 0u) {
+            if (tid == 0) {
+                mbar_expect_tx(bar, 4u * bytes);
+                for (int a = 0; a < 4; ++a) bulk_load_1d(base + a * arr_pitch, src[a] + goff, bytes, bar);
+            }
+            if (!mbar_wait_thread(bar, parity)) failed = true;
+            parity ^= 1u;
+            if (__syncthreads_or(failed)) {
                 failed = true;
                 break;
             }
-            parity[s] ^= 1u;
         } else {
-            __syncwarp();
-        }
-        const long long tile = blockIdx.x + n * gridDim.x;
-        const int rows = tile_rows_of(tile);
-        float* const sv = smem_f + (s * stage_bytes) / 4;
-        float* const sr = sv + arr_pitch / 4;
-        float* const sd = sr + arr_pitch / 4;
-        float* const swt = sd + arr_pitch / 4;
-        if (lane < rows) {
-            const int ro = lane * horizon;
-            float a_run = 0.0f, abs_run = 0.0f;
-            float v_n = sv[ro + horizon - 1];
-            for (int t = horizon - 2; t >= 0; --t) {
-                const float v_t = sv[ro + t];
-                a_run = adv_step(v_t, swt[ro + t], v_n, sr[ro + t + 1], sd[ro + t + 1], a_run, gamma,
-                                 gl, rho_clip, c_clip);
-                abs_run = __fadd_rn(abs_run, fabsf(a_run));
-                swt[ro + t] = a_run;
-                v_n = v_t;
+            for (int a = 0; a < 4; ++a) {
+                const float* g = src[a] + goff;
+                float* d = smem_f + (a * arr_pitch) / 4;
+                for (int e = tid; e < n_el; e += kB1Threads) d[e] = __ldg(g + e);
             }
-            if (seg_abs_sum != nullptr) seg_abs_sum[tile * tile_rows + lane] = abs_run;
+            __syncthreads();
         }
-        __syncwarp();
-        // coalesced copy-out, column H-1 of every row skipped
+        // ---- 2. terms, in place ----
+        // a thread owns groups of four consecutive elements (one 16-byte unit per
+        // array); the operand at e+4 comes from the next unit
+        uint32_t nonbin = 0u;
+        const int n_grp = (n_el + 3) >> 2;
+        const int grp_stride_cols = (4 * kB1Threads) % horizon;
+        int col_g = (4 * tid) % horizon;   // column of the first element of this thread's next group
+        for (int g0 = 0; g0 < n_grp; g0 += kB1Threads * kB1Batch) {
+            float4 dl4[kB1Batch], kk4[kB1Batch], gc4[kB1Batch], nn4[kB1Batch];
+#pragma unroll
+            for (int u = 0; u < kB1Batch; ++u) {
+                const int grp = g0 + u * kB1Threads + tid;
+                const int e = grp << 2;
+                float dl[4] = {0.0f, 0.0f, 0.0f, 0.0f}, kk[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                float gc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, nn[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+                if (grp < n_grp) {
+                    // the arrays are padded to 16 bytes, so a unit that straddles n_el is readable
+                    const float4 v4 = *reinterpret_cast<const float4*>(sv + e);
+                    const float4 r4 = *reinterpret_cast<const float4*>(sr + e);
+                    const float4 d4 = *reinterpret_cast<const float4*>(sd + e);
+                    const float4 w4 = *reinterpret_cast<const float4*>(swt + e);
+                    const bool more = e + 4 < n_el;
+                    const float vn = more ? sv[e + 4] : 0.0f;
+                    const float rn = more ? sr[e + 4] : 0.0f;
+                    const float dn = more ? sd[e + 4] : 0.0f;
+                    const float v[5] = {v4.x, v4.y, v4.z, v4.w, vn};
+                    const float r[5] = {r4.x, r4.y, r4.z, r4.w, rn};
+                    const float d[5] = {d4.x, d4.y, d4.z, d4.w, dn};
+                    const float w[4] = {w4.x, w4.y, w4.z, w4.w};
+                    int col = col_g;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const bool valid = (col < horizon - 1) && (e + j < n_el);   // then e+j+1 is in the same row
+                        float dj, gj, nj;
+                        adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
+                        dl[j] = valid ? dj : 0.0f;
+                        gc[j] = valid ? gj : 0.0f;
+                        nn[j] = valid ? nj : 1.0f;
+                        kk[j] = __fmul_rn(gc[j], nn[j]);
+                        nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nj)) : 0u;
+                        col = col + 1 == horizon ? 0 : col + 1;
+                    }
+                }
+                dl4[u] = make_float4(dl[0], dl[1], dl[2], dl[3]);
+                kk4[u] = make_float4(kk[0], kk[1], kk[2], kk[3]);
+                gc4[u] = make_float4(gc[0], gc[1], gc[2], gc[3]);
+                nn4[u] = make_float4(nn[0], nn[1], nn[2], nn[3]);
+                col_g += grp_stride_cols;
+                if (col_g >= horizon) col_g -= horizon;
+            }
+            __syncthreads();   // every operand of this batch has been read
+#pragma unroll
+            for (int u = 0; u < kB1Batch; ++u) {
+                const int grp = g0 + u * kB1Threads + tid;
+                const int e = grp << 2;
+                if (grp < n_grp) {
+                    *reinterpret_cast<float4*>(swt + e) = dl4[u];
+                    *reinterpret_cast<float4*>(sr + e) = kk4[u];
+                    *reinterpret_cast<float4*>(sd + e) = gc4[u];
+                    *reinterpret_cast<float4*>(sv + e) = nn4[u];
+                }
+            }
+        }
+        const bool any_nonbin = __syncthreads_or((nonbin << 1) != 0u);
+        // ---- 3. chain ----
+        if (tid < 32) {
+            const int lane = tid;
+            const int ro = lane * horizon;
+            const bool mine = lane < rows;
+            float a_run = 0.0f, abs_run = 0.0f, big = 0.0f;
+            bool literal = any_nonbin;
+            if (!literal) {
+                if (mine) {
+                    int t = horizon - 2;
+                    for (; t >= 7; t -= 8) {   // eight steps' operands first, then the dependent part
+                        float d8[8], k8[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            d8[j] = swt[ro + t - j];
+                            k8[j] = sr[ro + t - j];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            a_run = __fadd_rn(d8[j], __fmul_rn(k8[j], a_run));
+                            sr[ro + t - j] = a_run;
+                            abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                            big = fmaxf(big, fabsf(a_run));
+                        }
+                    }
+                    for (; t >= 0; --t) {
+                        a_run = __fadd_rn(swt[ro + t], __fmul_rn(sr[ro + t], a_run));
+                        sr[ro + t] = a_run;
+                        abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                        big = fmaxf(big, fabsf(a_run));
+                    }
+                }
+                literal = __any_sync(0xffffffffu, !(big <= 1e30f));
+            }
+            if (literal) {   // rare: the reference's literal order
+                a_run = 0.0f;
+                abs_run = 0.0f;
+                if (mine) {
+                    for (int t = horizon - 2; t >= 0; --t) {
+                        a_run = __fadd_rn(swt[ro + t], __fmul_rn(__fmul_rn(sd[ro + t], a_run), sv[ro + t]));
+                        sr[ro + t] = a_run;
+                        abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                    }
+                }
+            }
+            if (mine && seg_abs_sum != nullptr) seg_abs_sum[tile * tile_rows + lane] = abs_run;
+        }
+        __syncthreads();
+        // ---- 4. copy-out (advantages are in the r slot), column H-1 of every row skipped ----
         {
-            float* const g = advantages + tile * tile_elems;
-            const int n_el = rows * horizon;
-            const int n4 = n_el >> 2;   // tile start is 16-byte aligned
-            for (int e4 = lane; e4 < n4; e4 += 32) {
+            float* const g = advantages + goff;
+            const int n4 = n_el >> 2;   // the tile starts on a 16-byte boundary
+            int col = (4 * tid) % horizon;
+            for (int e4 = tid; e4 < n4; e4 += kB1Threads) {
                 const int e = e4 << 2;
-                const float4 a4 = *reinterpret_cast<const float4*>(swt + e);
-                const int col = e % horizon;
+                const float4 a4 = *reinterpret_cast<const float4*>(sr + e);
                 if (col + 4 < horizon) {
                     *reinterpret_cast<float4*>(g + e) = a4;
                 } else {
                     const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+                    int cj = col;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const int cj = (col + j) % horizon;
                         if (cj != horizon - 1) g[e + j] = av[j];
+                        cj = cj + 1 == horizon ? 0 : cj + 1;
                     }
                 }
+                col += grp_stride_cols;
+                if (col >= horizon) col -= horizon;
             }
-            for (int e = (n4 << 2) + lane; e < n_el; e += 32)
-                if (e % horizon != horizon - 1) g[e] = swt[e];
+            for (int e = (n4 << 2) + tid; e < n_el; e += kB1Threads)
+                if (e % horizon != horizon - 1) g[e] = sr[e];
         }
-        // the stage is refilled by the async proxy two iterations from now
+        // the stage is refilled by the async proxy next
         fence_proxy_async();
-        __syncwarp();
+        __syncthreads();
     }
-    if (failed && lane == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+    if (failed && tid == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
 }
 
 // ---------------------------------------------------------------------------
@@ -869,6 +1290,13 @@ static void set_tma2d_attrs()
     cudaFuncSetAttribute(puff_adv_tma2d_kernel<NST, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_smem_bytes<NST>());
 }
 
+template <int NST, int NT>
+static void set_tma2d_ws_attrs()
+{
+    cudaFuncSetAttribute(puff_adv_tma2d_ws_kernel<NST, NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_ws_smem_bytes<NST, NT>());
+    cudaFuncSetAttribute(puff_adv_tma2d_ws_kernel<NST, NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma2d_ws_smem_bytes<NST, NT>());
+}
+
 static const DeviceInfo* device_info(int* code)
 {
     int dev = 0;
@@ -897,6 +1325,14 @@ static const DeviceInfo* device_info(int* code)
                 set_tma2d_attrs<6>();
                 set_tma2d_attrs<8>();
                 set_tma2d_attrs<12>();
+                set_tma2d_ws_attrs<3, 2>();
+                set_tma2d_ws_attrs<4, 2>();
+                set_tma2d_ws_attrs<5, 2>();
+                set_tma2d_ws_attrs<6, 2>();
+                set_tma2d_ws_attrs<8, 2>();
+                set_tma2d_ws_attrs<10, 2>();
+                set_tma2d_ws_attrs<4, 3>();
+                set_tma2d_ws_attrs<8, 3>();
                 cudaFuncSetAttribute(puff_adv_bulk1d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem_optin);
                 d.err = cudaGetLastError();
             }
@@ -976,14 +1412,30 @@ static cudaError_t launch_tma2d(const MapSet& m, float* seg_abs_sum, float gamma
     return cudaGetLastError();
 }
 
+template <int NST, int NT>
+static cudaError_t launch_tma2d_ws(const MapSet& m, float* seg_abs_sum, float gamma, float lambda, float rho_clip,
+                                   float c_clip, long long rows, int horizon, int grid, int tiles, cudaStream_t st)
+{
+    if (seg_abs_sum != nullptr)
+        puff_adv_tma2d_ws_kernel<NST, NT, true><<<grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st>>>(
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[4], seg_abs_sum, gamma, lambda, rho_clip, c_clip,
+            rows, horizon, tiles);
+    else
+        puff_adv_tma2d_ws_kernel<NST, NT, false><<<grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st>>>(
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[4], nullptr, gamma, lambda, rho_clip, c_clip,
+            rows, horizon, tiles);
+    return cudaGetLastError();
+}
+
 static bool ranges_overlap(const void* a, size_t na, const void* b, size_t nb)
 {
     const uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
     return a0 < b0 + nb && b0 < a0 + na;
 }
 
-// bulk1d tile height: the largest of 32/16/8/4 rows whose two stages stay
-// within ~40 KB (so that several CTAs share an SM), else whatever still fits
+// bulk1d tile height: 32 rows when one stage stays within ~72 KB (three CTAs
+// per SM), otherwise the largest of 16/8/4 rows that does, otherwise the largest
+// that fits at all; 0 when even four rows do not fit
 static int bulk1d_tile_rows(long long horizon, int max_smem, size_t* smem_bytes)
 {
     const int cand[4] = {32, 16, 8, 4};
@@ -991,19 +1443,17 @@ static int bulk1d_tile_rows(long long horizon, int max_smem, size_t* smem_bytes)
     size_t best_bytes = 0;
     for (int i = 0; i < 4; ++i) {
         const size_t arr = (static_cast<size_t>(cand[i]) * horizon * 4 + 15) & ~static_cast<size_t>(15);
-        const size_t need = 2 * 4 * arr + 16 + 128;
+        const size_t need = 4 * arr + 16 + 128;
         if (need > static_cast<size_t>(max_smem)) continue;
         if (best == 0) {
             best = cand[i];
             best_bytes = need;
         }
-        if (need <= 40 * 1024) {
+        if (need <= 72 * 1024) {
             best = cand[i];
             best_bytes = need;
             break;
         }
-        best = cand[i];
-        best_bytes = need;
     }
     *smem_bytes = best_bytes;
     return best;
@@ -1114,9 +1564,35 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
                 cache.horizon = horizon;
             }
             const long long tiles = (rows + kTileRows - 1) / kTileRows;
+            float* abs_p = seg_abs_sum != nullptr ? seg_abs_sum + r0 : nullptr;
+            // Large buffers: the warp-specialised kernel (three stages, two terms buffers,
+            // two CTAs per SM measured best on 131072 x 256).  Buffers of only a few tiles
+            // per SM finish sooner on the single-warp kernel, whose pipeline has fewer hops.
+            // PUFF_ADV_WS: 0 = single-warp, 10*NST + NT = warp-specialised with that shape.
+            const int ws = env_int("PUFF_ADV_WS", tiles >= 4LL * dev->sm_count ? 32 : 0);
+            if (ws != 0) {
+                int wnst = ws >= 10 ? ws / 10 : 3, wnt = ws >= 10 ? ws % 10 : 2;
+                const int smem = wnt == 3 ? (wnst >= 8 ? tma2d_ws_smem_bytes<8, 3>() : tma2d_ws_smem_bytes<4, 3>())
+                                          : (wnst * kStageBytes + 2 * kTermBytes + kWsOutSlots * kBoxBytes + 2048);
+                int per_sm = (dev->max_smem_optin + 1024) / (smem + 1024);
+                { const int o = env_int("PUFF_ADV_CTAS_PER_SM", 0); if (o > 0 && o < per_sm) per_sm = o; }
+                if (per_sm < 1) per_sm = 1;
+                const long long mg = static_cast<long long>(dev->sm_count) * per_sm;
+                const int grid = static_cast<int>(tiles < mg ? tiles : mg);
+#define PUFF_WS_CASE(A, B) err = launch_tma2d_ws<A, B>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st)
+                if (wnt == 3) { if (wnst >= 8) PUFF_WS_CASE(8, 3); else PUFF_WS_CASE(4, 3); }
+                else if (wnst <= 3) PUFF_WS_CASE(3, 2);
+                else if (wnst == 4) PUFF_WS_CASE(4, 2);
+                else if (wnst == 5) PUFF_WS_CASE(5, 2);
+                else if (wnst <= 6) PUFF_WS_CASE(6, 2);
+                else if (wnst <= 8) PUFF_WS_CASE(8, 2);
+                else PUFF_WS_CASE(10, 2);
+#undef PUFF_WS_CASE
+                g_launch_count.fetch_add(1, std::memory_order_relaxed);
+                continue;
+            }
             const long long max_grid = static_cast<long long>(dev->sm_count) * ctas_per_sm;
             const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
-            float* abs_p = seg_abs_sum != nullptr ? seg_abs_sum + r0 : nullptr;
 #define PUFF_TMA2D_CASE(N)                                                                               \
     err = launch_tma2d<N>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, \
                           static_cast<int>(tiles), st)
@@ -1133,12 +1609,13 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
         }
     } else if (kernel == PUFF_KERNEL_BULK1D) {
         const long long tiles = (num_segments + bulk_rows - 1) / bulk_rows;
-        const int per_sm = static_cast<int>(static_cast<size_t>(dev->max_smem_optin) / (bulk_smem + 1024));
-        const long long max_grid = static_cast<long long>(dev->sm_count) * (per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm));
+        int per_sm = static_cast<int>(static_cast<size_t>(dev->max_smem_optin + 1024) / (bulk_smem + 1024));
+        per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+        const long long max_grid = static_cast<long long>(dev->sm_count) * per_sm;
         const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
-        puff_adv_bulk1d_kernel<<<grid, 32, bulk_smem, st>>>(values, rewards, dones, importance, advantages,
-                                                            seg_abs_sum, gamma, lambda, rho_clip, c_clip,
-                                                            num_segments, static_cast<int>(horizon), bulk_rows, tiles);
+        puff_adv_bulk1d_kernel<<<grid, kB1Threads, bulk_smem, st>>>(values, rewards, dones, importance, advantages,
+                                                                    seg_abs_sum, gamma, lambda, rho_clip, c_clip,
+                                                                    num_segments, static_cast<int>(horizon), bulk_rows, tiles);
         err = cudaGetLastError();
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
     } else if (kernel == PUFF_KERNEL_SCAN) {
