@@ -62,13 +62,38 @@ class ShardedAdvantage:
     def local_segments(self):
         return self.hi - self.lo
 
-    def step(self, values, rewards, dones, importance, advantages, seg_abs_sum):
-        """All tensors are this rank's rows [local_segments, horizon] (and
-        [local_segments] for seg_abs_sum).  Returns (probs, total) where total
-        is the global weight sum as a 1-element fp64 tensor."""
+    def priorities(self, seg_abs_sum):
+        """Local weights, their all-reduced total, globally normalised probabilities."""
         k = self.kernels
-        k.advantage_prio(values, rewards, dones, importance, advantages, seg_abs_sum, self.hyper)
         weights, total = k.weights(seg_abs_sum, self.prio_alpha)
         if self.world > 1:
             dist.all_reduce(total, op=dist.ReduceOp.SUM, group=self.group)
         return k.probs(weights, total), total
+
+    def step_overlapped(self, values, rewards, dones, importance, advantages, seg_abs_sum, side_stream):
+        """CUDA only.  The advantage kernel goes to the current stream; the
+        priority launches and the all-reduce of their scalar go to
+        `side_stream`, ordered after the kernel by an event, so that they
+        overlap whatever the caller enqueues next on the current stream (for
+        instance the next advantage pass on other buffers).
+
+        Returns (probs, total, done): `done` is an event on the side stream.
+        The caller must make a stream wait on it before that stream reads
+        `probs`/`total` or overwrites `seg_abs_sum`."""
+        main = torch.cuda.current_stream()
+        self.kernels.advantage_prio(values, rewards, dones, importance, advantages, seg_abs_sum, self.hyper)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(side_stream):
+            side_stream.wait_event(ready)
+            probs, total = self.priorities(seg_abs_sum)
+            done = torch.cuda.Event()
+            done.record(side_stream)
+        return probs, total, done
+
+    def step(self, values, rewards, dones, importance, advantages, seg_abs_sum):
+        """All tensors are this rank's rows [local_segments, horizon] (and
+        [local_segments] for seg_abs_sum).  Returns (probs, total) where total
+        is the global weight sum as a 1-element fp64 tensor."""
+        self.kernels.advantage_prio(values, rewards, dones, importance, advantages, seg_abs_sum, self.hyper)
+        return self.priorities(seg_abs_sum)
