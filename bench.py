@@ -465,7 +465,8 @@ def run_b200_arm(args, wl, rank, local_rank, world):
             "timing": timing,
             "reference_cuda_kernel": ref_cuda,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": TRAFFIC.get((wl.name, kernel_name)),
+                         "frac": achieved / peak,
+                         "traffic": TRAFFIC.get((wl.name, kernel_name)) if wl.segments == WORKLOADS[wl.name].segments else None,
                          "kernel": kernel_name, "kernel_ms": kernel_ms, "peak_kind": f"of {peak_kind}",
                          "algorithmic_bytes": BYTES_PER_ELEMENT * elems},
             "e2e": e2e,
@@ -511,9 +512,12 @@ def time_reference_cuda_kernel(sets, n_sets, hyper, elems):
         return {"error": str(exc)[:200]}
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the
-# ncu captures summarised under profiles/; None until a capture exists.
-TRAFFIC = {}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant
+# kernel from the ncu capture summarised in
+# profiles/tma2d_ws_kernel_cfg2_32768x256_ncu_full.md: 138.44 MB read + 16.32 MB written
+# on a 32768-segment case, scaled by the rows of a full launch (every row is read once,
+# so traffic grows in proportion).
+TRAFFIC = {("cfg2", "tma2d"): int((138.44e6 + 16.32e6) * 4)}
 
 
 def main():
