@@ -44,6 +44,7 @@ from pufferlib_b200.workloads import WORKLOADS, make_inputs  # noqa: E402
 L2_BYTES = 126 * 1024 * 1024
 BYTES_PER_ELEMENT = 20          # 4 fp32 inputs read + 1 fp32 output written
 PRIO_ALPHA = 0.8                # config/default.ini:60
+DEPTH = 3                       # steps whose side-stream work may be outstanding
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -259,7 +260,10 @@ def run_b200_arm(args, wl, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # the tiny all-reduce has to slip in between persistent advantage kernels that
+        # fill every SM: give NCCL's stream (and the side stream below) high priority
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
 
     S, H = wl.segments, wl.horizon
     hyper = wl.hyper()
@@ -271,13 +275,13 @@ def run_b200_arm(args, wl, rank, local_rank, world):
     sets = []
     for i in range(n_sets):
         ins = [t.to(dev) for t in host] if i == 0 else [t.clone() for t in sets[0][:4]]
-        # two sum buffers per set: the priority launches of step i read one on the side
-        # stream while the advantage kernel of step i+1 fills the other
-        sets.append(ins + [torch.zeros((S, H), device=dev), (torch.empty(S, device=dev), torch.empty(S, device=dev))])
+        # DEPTH sum buffers per set: the priority launches of step i read one on the side
+        # stream while the advantage kernels of the following steps fill the others
+        sets.append(ins + [torch.zeros((S, H), device=dev), tuple(torch.empty(S, device=dev) for _ in range(DEPTH))])
     sharded = ShardedAdvantage(S * world, H, hyper, PRIO_ALPHA, rank=rank, world=world)
     variant = args.variant
     os.environ["PUFFER_ADV_VARIANT"] = variant
-    side_stream = torch.cuda.Stream()
+    side_stream = torch.cuda.Stream(priority=-1)
     pending = collections.deque()
     last = {}
 
@@ -286,17 +290,17 @@ def run_b200_arm(args, wl, rank, local_rank, world):
         weights / all-reduce / probabilities behind it on the side stream."""
         v, r, d, w, adv, abs2 = sets[i % n_sets]
         main = torch.cuda.current_stream()
-        while len(pending) >= 2:          # the sum buffer of step i-2 is free again
+        while len(pending) >= DEPTH:      # the sum buffer of step i-DEPTH is free again
             main.wait_event(pending.popleft())
         if ev is not None:
             ev[0].record()
         if args.no_overlap:
-            sharded.kernels.advantage_prio(v, r, d, w, adv, abs2[i & 1], hyper)
+            sharded.kernels.advantage_prio(v, r, d, w, adv, abs2[i % DEPTH], hyper)
             if ev is not None:
                 ev[1].record()
-            last["probs"], last["total"] = sharded.priorities(abs2[i & 1])
+            last["probs"], last["total"] = sharded.priorities(abs2[i % DEPTH])
             return
-        probs, total, done = sharded.step_overlapped(v, r, d, w, adv, abs2[i & 1], side_stream)
+        probs, total, done = sharded.step_overlapped(v, r, d, w, adv, abs2[i % DEPTH], side_stream)
         if ev is not None:
             ev[1].record()      # recorded on the main stream: brackets the advantage kernel only
         pending.append(done)
@@ -326,7 +330,7 @@ def run_b200_arm(args, wl, rank, local_rank, world):
 
     def adv_only(i):
         v, r, d, w, adv, abs2 = sets[i % n_sets]
-        sharded.kernels.advantage_prio(v, r, d, w, adv, abs2[i & 1], hyper)
+        sharded.kernels.advantage_prio(v, r, d, w, adv, abs2[i % DEPTH], hyper)
 
     # The timed loop is captured into CUDA graphs and replayed: a buffer set that fits
     # L2 many times over makes a step of a few microseconds, and with N > 1 the per-step
