@@ -78,6 +78,24 @@ int puff_advantage_sm100_launch(const float* values, const float* rewards,
                                 int variant, void* cuda_stream);
 
 /*
+ * puff_advantage_sm100_launch with option flags.
+ *
+ * PUFF_FLAG_ZERO_LAST_COLUMN: the op owns the whole output and also writes
+ * advantages[:, horizon-1] = 0, so `advantages` may be uninitialised memory.
+ * This is the contract change that lets the trainer drop the `torch.zeros`
+ * fill in front of every call (pufferl.py:352-353: one extra 4 B/element write
+ * pass and one launch per minibatch); the 9-argument reference contract, which
+ * leaves that column alone, stays on puff_advantage_sm100_launch (flags = 0).
+ */
+#define PUFF_FLAG_ZERO_LAST_COLUMN 1u
+int puff_advantage_sm100_launch_ex(const float* values, const float* rewards,
+                                   const float* dones, const float* importance,
+                                   float* advantages, float* seg_abs_sum,
+                                   float gamma, float lambda, float rho_clip, float c_clip,
+                                   long long num_segments, long long horizon,
+                                   int variant, unsigned flags, void* cuda_stream);
+
+/*
  * The same op on HOST buffers (pinned memory recommended), synchronous.
  *
  * Stands where the reference's host-tensor path stands: the Python wrapper's

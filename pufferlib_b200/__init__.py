@@ -9,6 +9,7 @@ __version__ = "0.1"
 
 from .advantage import (  # noqa: F401
     compute_puff_advantage,
+    compute_puff_advantage_fill,
     compute_puff_advantage_host,
     compute_puff_advantage_prio,
     prioritized_sample_probs,

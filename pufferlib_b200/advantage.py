@@ -44,6 +44,20 @@ def compute_puff_advantage_prio(values, rewards, terminals, ratio, advantages, s
     return advantages, seg_abs_sum
 
 
+def compute_puff_advantage_fill(values, rewards, terminals, ratio, gamma, gae_lambda,
+                                vtrace_rho_clip, vtrace_c_clip, advantages=None, seg_abs_sum=None):
+    """The op with ownership of its whole output: writes advantages[:, H-1] = 0
+    itself, so no zero-filled buffer is needed in front of it (replaces the
+    `torch.zeros` + op pair of pufferl.py:352-356 and saves one 4 B/element
+    write pass per call).  `advantages` may be any uninitialised [S, H] fp32
+    tensor; one is allocated when omitted.  Returns it."""
+    if advantages is None:
+        advantages = torch.empty_like(values)
+    _ops().compute_puff_advantage_fill(values, rewards, terminals, ratio, advantages, seg_abs_sum,
+                                       gamma, gae_lambda, vtrace_rho_clip, vtrace_c_clip)
+    return advantages
+
+
 def priority_weights(seg_abs_sum, prio_alpha):
     """(weights, total): weights = nan_to_num(seg_abs_sum ** alpha, 0, 0, 0)
     (pufferl.py:360) and their fp64 sum as a 1-element CUDA tensor."""
@@ -97,7 +111,7 @@ def compute_puff_advantage_host(values, rewards, terminals, ratio, advantages,
 
 
 def launch_raw(values, rewards, terminals, ratio, advantages, gamma, gae_lambda,
-               vtrace_rho_clip, vtrace_c_clip, seg_abs_sum=None, variant="auto", stream=None):
+               vtrace_rho_clip, vtrace_c_clip, seg_abs_sum=None, variant="auto", stream=None, flags=0):
     """Direct C-ABI launch on CUDA tensors (no dispatcher): used by tests and
     the benchmark to pick a kernel variant explicitly.  Only pointers and sizes
     cross the boundary; shapes are the caller's responsibility."""
@@ -105,9 +119,9 @@ def launch_raw(values, rewards, terminals, ratio, advantages, gamma, gae_lambda,
     S, H = values.shape
     if stream is None:
         stream = torch.cuda.current_stream(values.device).cuda_stream
-    rc = lib.puff_advantage_sm100_launch(
+    rc = lib.puff_advantage_sm100_launch_ex(
         values.data_ptr(), rewards.data_ptr(), terminals.data_ptr(), ratio.data_ptr(),
         advantages.data_ptr(), None if seg_abs_sum is None else seg_abs_sum.data_ptr(),
-        gamma, gae_lambda, vtrace_rho_clip, vtrace_c_clip, S, H, cabi.VARIANTS[variant], stream)
-    cabi.check(rc, "puff_advantage_sm100_launch")
+        gamma, gae_lambda, vtrace_rho_clip, vtrace_c_clip, S, H, cabi.VARIANTS[variant], flags, stream)
+    cabi.check(rc, "puff_advantage_sm100_launch_ex")
     return advantages

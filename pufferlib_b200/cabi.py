@@ -18,6 +18,7 @@ OK = 0
 ERR_NULL, ERR_SHAPE, ERR_VARIANT, ERR_ALIGN, ERR_ALIAS = -1, -2, -3, -4, -5
 ERR_ARCH, ERR_DRIVER, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_SIZE = -6, -7, -8, -9, -10
 NOALLOC_MAX_SEGMENTS = 524288
+FLAG_ZERO_LAST_COLUMN = 1
 VARIANT_AUTO, VARIANT_SERIAL, VARIANT_SCAN, VARIANT_GENERIC = 0, 1, 2, 3
 KERNEL_NONE, KERNEL_TMA2D, KERNEL_BULK1D, KERNEL_SCAN, KERNEL_GENERIC = 0, 1, 2, 3, 4
 VARIANTS = {"auto": VARIANT_AUTO, "serial": VARIANT_SERIAL, "scan": VARIANT_SCAN, "generic": VARIANT_GENERIC}
@@ -31,6 +32,7 @@ _LL = ctypes.c_longlong
 _I = ctypes.c_int
 SIGNATURES = {
     "puff_advantage_sm100_launch": (_I, [_P] * 6 + [_F] * 4 + [_LL, _LL, _I, _P]),
+    "puff_advantage_sm100_launch_ex": (_I, [_P] * 6 + [_F] * 4 + [_LL, _LL, _I, ctypes.c_uint, _P]),
     "puff_advantage_sm100_host": (_I, [_P] * 6 + [_F] * 4 + [_LL, _LL, _I, _I]),
     "puff_advantage_sm100_host_release": (_I, [_I]),
     "puff_priorities_sm100_scratch_bytes": (ctypes.c_size_t, [_LL]),

@@ -433,7 +433,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
     for (int i = 0; i < total; ++i) {
         if (c == nchunks - 1) {   // new tile
             const long long row = (static_cast<long long>(blockIdx.x) + static_cast<long long>(k) * gridDim.x) * kTileRows + lane;
-            keep_last = row < num_segments ? adv_in[row * horizon + horizon - 1] : 0.0f;
+            keep_last = (adv_in != nullptr && row < num_segments) ? adv_in[row * horizon + horizon - 1] : 0.0f;
             a_run = 0.0f;
             abs_run = 0.0f;
         }
@@ -744,7 +744,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
             if (c == nchunks - 1) {   // tile start
                 const long long row = static_cast<long long>(tile) * kTileRows + lane;
-                keep_last = row < num_segments ? adv_in[row * horizon + horizon - 1] : 0.0f;
+                keep_last = (adv_in != nullptr && row < num_segments) ? adv_in[row * horizon + horizon - 1] : 0.0f;
                 a_run = 0.0f;
                 abs_run = 0.0f;
             }
@@ -866,7 +866,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                        const float* __restrict__ dones, const float* __restrict__ importance,
                        float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
                        float lambda, float rho_clip, float c_clip, long long num_segments,
-                       int horizon, int tile_rows, long long num_tiles)
+                       int horizon, int tile_rows, long long num_tiles, int zero_last)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
@@ -1046,14 +1046,17 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         if (cj != horizon - 1) g[e + j] = av[j];
+                        else if (zero_last) g[e + j] = 0.0f;
                         cj = cj + 1 == horizon ? 0 : cj + 1;
                     }
                 }
                 col += grp_stride_cols;
                 if (col >= horizon) col -= horizon;
             }
-            for (int e = (n4 << 2) + tid; e < n_el; e += kB1Threads)
+            for (int e = (n4 << 2) + tid; e < n_el; e += kB1Threads) {
                 if (e % horizon != horizon - 1) g[e] = sr[e];
+                else if (zero_last) g[e] = 0.0f;
+            }
         }
         // the stage is refilled by the async proxy next
         fence_proxy_async();
@@ -1077,7 +1080,8 @@ __global__ void __launch_bounds__(1024)
 puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
                      const float* __restrict__ dones, const float* __restrict__ importance,
                      float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
-                     float lambda, float rho_clip, float c_clip, long long num_segments, int horizon)
+                     float lambda, float rho_clip, float c_clip, long long num_segments, int horizon,
+                     int zero_last)
 {
     __shared__ float s_k[32], s_d[32], s_abs[32];
     __shared__ float s_carry;
@@ -1099,6 +1103,7 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
         float* const a = advantages + ro;
         float a_pass = 0.0f;      // advantage entering this pass (from later columns)
         float abs_acc = 0.0f;     // thread 0 only
+        if (zero_last && tid == 0) a[horizon - 1] = 0.0f;
 
         for (int p = 0; p < passes; ++p) {
             const int j = p * nt + tid;
@@ -1250,7 +1255,7 @@ puff_adv_generic_kernel(const float* __restrict__ values, const float* __restric
                         const float* __restrict__ dones, const float* __restrict__ importance,
                         float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
                         float lambda, float rho_clip, float c_clip, long long num_segments,
-                        long long horizon)
+                        long long horizon, int zero_last)
 {
     const float gl = __fmul_rn(gamma, lambda);
     for (long long row = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -1266,6 +1271,7 @@ puff_adv_generic_kernel(const float* __restrict__ values, const float* __restric
             advantages[ro + t] = a_run;
             v_n = v_t;
         }
+        if (zero_last) advantages[ro + horizon - 1] = 0.0f;
         if (seg_abs_sum != nullptr) seg_abs_sum[row] = abs_run;
     }
 }
@@ -1398,31 +1404,31 @@ static int env_int(const char* name, int fallback)
 }
 
 template <int NST>
-static cudaError_t launch_tma2d(const MapSet& m, float* seg_abs_sum, float gamma, float lambda, float rho_clip,
+static cudaError_t launch_tma2d(const MapSet& m, const float* adv_in, float* seg_abs_sum, float gamma, float lambda, float rho_clip,
                                 float c_clip, long long rows, int horizon, int grid, int tiles, cudaStream_t st)
 {
     if (seg_abs_sum != nullptr)
         puff_adv_tma2d_kernel<NST, true><<<grid, 32, tma2d_smem_bytes<NST>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[4], seg_abs_sum, gamma, lambda, rho_clip, c_clip,
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], adv_in, seg_abs_sum, gamma, lambda, rho_clip, c_clip,
             rows, horizon, tiles);
     else
         puff_adv_tma2d_kernel<NST, false><<<grid, 32, tma2d_smem_bytes<NST>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[4], nullptr, gamma, lambda, rho_clip, c_clip,
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], adv_in, nullptr, gamma, lambda, rho_clip, c_clip,
             rows, horizon, tiles);
     return cudaGetLastError();
 }
 
 template <int NST, int NT>
-static cudaError_t launch_tma2d_ws(const MapSet& m, float* seg_abs_sum, float gamma, float lambda, float rho_clip,
+static cudaError_t launch_tma2d_ws(const MapSet& m, const float* adv_in, float* seg_abs_sum, float gamma, float lambda, float rho_clip,
                                    float c_clip, long long rows, int horizon, int grid, int tiles, cudaStream_t st)
 {
     if (seg_abs_sum != nullptr)
         puff_adv_tma2d_ws_kernel<NST, NT, true><<<grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[4], seg_abs_sum, gamma, lambda, rho_clip, c_clip,
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], adv_in, seg_abs_sum, gamma, lambda, rho_clip, c_clip,
             rows, horizon, tiles);
     else
         puff_adv_tma2d_ws_kernel<NST, NT, false><<<grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[4], nullptr, gamma, lambda, rho_clip, c_clip,
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], adv_in, nullptr, gamma, lambda, rho_clip, c_clip,
             rows, horizon, tiles);
     return cudaGetLastError();
 }
@@ -1469,15 +1475,32 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
                                            long long num_segments, long long horizon, int variant,
                                            void* cuda_stream)
 {
+    return puff_advantage_sm100_launch_ex(values, rewards, dones, importance, advantages, seg_abs_sum, gamma, lambda,
+                                          rho_clip, c_clip, num_segments, horizon, variant, 0u, cuda_stream);
+}
+
+extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* rewards, const float* dones,
+                                              const float* importance, float* advantages, float* seg_abs_sum,
+                                              float gamma, float lambda, float rho_clip, float c_clip,
+                                              long long num_segments, long long horizon, int variant,
+                                              unsigned flags, void* cuda_stream)
+{
     t_last_kernel = PUFF_KERNEL_NONE;
     if (num_segments < 0 || horizon < 0) return PUFF_ERR_SHAPE;
     if (variant < PUFF_VARIANT_AUTO || variant > PUFF_VARIANT_GENERIC) return PUFF_ERR_VARIANT;
+    if (flags & ~static_cast<unsigned>(PUFF_FLAG_ZERO_LAST_COLUMN)) return PUFF_ERR_VARIANT;
+    const int zero_last = (flags & PUFF_FLAG_ZERO_LAST_COLUMN) ? 1 : 0;
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     if (num_segments == 0) return PUFF_OK;
     if (horizon < 2) {
-        // no step exists: nothing is written to advantages, the sums are empty
+        // no step exists: the sums are empty, and advantages is written only when the op owns column H-1
         if (seg_abs_sum != nullptr) {
             cudaError_t e = cudaMemsetAsync(seg_abs_sum, 0, static_cast<size_t>(num_segments) * 4, st);
+            if (e != cudaSuccess) return static_cast<int>(e);
+        }
+        if (zero_last && horizon == 1) {
+            if (advantages == nullptr) return PUFF_ERR_NULL;
+            cudaError_t e = cudaMemsetAsync(advantages, 0, static_cast<size_t>(num_segments) * 4, st);
             if (e != cudaSuccess) return static_cast<int>(e);
         }
         return PUFF_OK;
@@ -1579,7 +1602,7 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
                 if (per_sm < 1) per_sm = 1;
                 const long long mg = static_cast<long long>(dev->sm_count) * per_sm;
                 const int grid = static_cast<int>(tiles < mg ? tiles : mg);
-#define PUFF_WS_CASE(A, B) err = launch_tma2d_ws<A, B>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st)
+#define PUFF_WS_CASE(A, B) err = launch_tma2d_ws<A, B>(cache, zero_last ? nullptr : p[4], abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st)
                 if (wnt == 3) { if (wnst >= 8) PUFF_WS_CASE(8, 3); else PUFF_WS_CASE(4, 3); }
                 else if (wnst <= 3) PUFF_WS_CASE(3, 2);
                 else if (wnst == 4) PUFF_WS_CASE(4, 2);
@@ -1594,7 +1617,7 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
             const long long max_grid = static_cast<long long>(dev->sm_count) * ctas_per_sm;
             const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
 #define PUFF_TMA2D_CASE(N)                                                                               \
-    err = launch_tma2d<N>(cache, abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, \
+    err = launch_tma2d<N>(cache, zero_last ? nullptr : p[4], abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, \
                           static_cast<int>(tiles), st)
             switch (nst) {
                 case 2: PUFF_TMA2D_CASE(2); break;
@@ -1615,7 +1638,7 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
         const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
         puff_adv_bulk1d_kernel<<<grid, kB1Threads, bulk_smem, st>>>(values, rewards, dones, importance, advantages,
                                                                     seg_abs_sum, gamma, lambda, rho_clip, c_clip,
-                                                                    num_segments, static_cast<int>(horizon), bulk_rows, tiles);
+                                                                    num_segments, static_cast<int>(horizon), bulk_rows, tiles, zero_last);
         err = cudaGetLastError();
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
     } else if (kernel == PUFF_KERNEL_SCAN) {
@@ -1626,10 +1649,10 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
         const int grid = static_cast<int>(num_segments < max_grid ? num_segments : max_grid);
         if (aligned16 && horizon % 4 == 0)
             puff_adv_scan_kernel<true><<<grid, nt, 0, st>>>(values, rewards, dones, importance, advantages, seg_abs_sum,
-                                                            gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon));
+                                                            gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon), zero_last);
         else
             puff_adv_scan_kernel<false><<<grid, nt, 0, st>>>(values, rewards, dones, importance, advantages, seg_abs_sum,
-                                                             gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon));
+                                                             gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon), zero_last);
         err = cudaGetLastError();
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
     } else {
@@ -1637,7 +1660,7 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
         const long long max_grid = static_cast<long long>(dev->sm_count) * 16;
         const int grid = static_cast<int>(blocks < max_grid ? blocks : max_grid);
         puff_adv_generic_kernel<<<grid, 128, 0, st>>>(values, rewards, dones, importance, advantages, seg_abs_sum,
-                                                      gamma, lambda, rho_clip, c_clip, num_segments, horizon);
+                                                      gamma, lambda, rho_clip, c_clip, num_segments, horizon, zero_last);
         err = cudaGetLastError();
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
     }

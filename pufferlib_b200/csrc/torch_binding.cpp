@@ -21,6 +21,7 @@
 #include <torch/library.h>
 
 #include <cstdlib>
+#include <optional>
 #include <tuple>
 
 #include "../../include/puff_advantage.h"
@@ -118,6 +119,37 @@ void compute_puff_advantage_prio_cuda(torch::Tensor values, torch::Tensor reward
     check_rc(rc, "compute_puff_advantage_prio");
 }
 
+// The op with ownership of the whole output: also writes advantages[:, H-1] = 0,
+// so the caller may pass torch.empty instead of the torch.zeros of pufferl.py:352-353.
+// seg_abs_sum is optional.
+void compute_puff_advantage_fill_cuda(torch::Tensor values, torch::Tensor rewards, torch::Tensor dones,
+                                      torch::Tensor importance, torch::Tensor advantages,
+                                      std::optional<torch::Tensor> seg_abs_sum, double gamma, double lambda,
+                                      double rho_clip, double c_clip)
+{
+    check_inputs({values, rewards, dones, importance, advantages}, values);
+    float* abs_ptr = nullptr;
+    if (seg_abs_sum.has_value()) {
+        const torch::Tensor& t = *seg_abs_sum;
+        TORCH_CHECK(t.dim() == 1 && t.size(0) == values.size(0), "seg_abs_sum must be 1D with one entry per segment");
+        TORCH_CHECK(t.device() == values.device(), "All tensors must be on same device");
+        TORCH_CHECK(t.dtype() == torch::kFloat32, "All tensors must be float32");
+        TORCH_CHECK(t.is_contiguous(), "All tensors must be contiguous");
+        abs_ptr = t.data_ptr<float>();
+    }
+    int rc;
+    {
+        const c10::cuda::CUDAGuard guard(values.device());
+        rc = puff_advantage_sm100_launch_ex(
+            values.data_ptr<float>(), rewards.data_ptr<float>(), dones.data_ptr<float>(),
+            importance.data_ptr<float>(), advantages.data_ptr<float>(), abs_ptr,
+            static_cast<float>(gamma), static_cast<float>(lambda), static_cast<float>(rho_clip),
+            static_cast<float>(c_clip), values.size(0), values.size(1), variant_from_env(),
+            PUFF_FLAG_ZERO_LAST_COLUMN, at::cuda::getCurrentCUDAStream().stream());
+    }
+    check_rc(rc, "compute_puff_advantage_fill");
+}
+
 // pufferl.py:360 plus the sum of :361: weights and their fp64 total.
 std::tuple<torch::Tensor, torch::Tensor> puff_priority_weights_cuda(torch::Tensor seg_abs_sum, double alpha)
 {
@@ -165,6 +197,7 @@ TORCH_LIBRARY(pufferlib, m)
     // byte-identical to pufferlib.cpp:88
     m.def("compute_puff_advantage(Tensor(a!) values, Tensor(b!) rewards, Tensor(c!) dones, Tensor(d!) importance, Tensor(e!) advantages, float gamma, float lambda, float rho_clip, float c_clip) -> ()");
     m.def("compute_puff_advantage_prio(Tensor values, Tensor rewards, Tensor dones, Tensor importance, Tensor(a!) advantages, Tensor(b!) seg_abs_sum, float gamma, float lambda, float rho_clip, float c_clip) -> ()");
+    m.def("compute_puff_advantage_fill(Tensor values, Tensor rewards, Tensor dones, Tensor importance, Tensor(a!) advantages, Tensor(b!)? seg_abs_sum, float gamma, float lambda, float rho_clip, float c_clip) -> ()");
     m.def("puff_priority_weights(Tensor seg_abs_sum, float alpha) -> (Tensor, Tensor)");
     m.def("puff_priority_probs(Tensor weights, Tensor total_w) -> Tensor");
 }
@@ -173,6 +206,7 @@ TORCH_LIBRARY_IMPL(pufferlib, CUDA, m)
 {
     m.impl("compute_puff_advantage", &compute_puff_advantage_cuda);
     m.impl("compute_puff_advantage_prio", &compute_puff_advantage_prio_cuda);
+    m.impl("compute_puff_advantage_fill", &compute_puff_advantage_fill_cuda);
     m.impl("puff_priority_weights", &puff_priority_weights_cuda);
     m.impl("puff_priority_probs", &puff_priority_probs_cuda);
 }

@@ -25,7 +25,7 @@ def _clear_force():
     os.environ.pop("PUFF_ADV_STAGES", None)
 
 
-def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=SENTINEL, stages=None):
+def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=SENTINEL, stages=None, flags=0):
     """Launch through the C ABI; returns (advantages, abs_sum or None, kernel name)."""
     from pufferlib_b200 import cabi
     from pufferlib_b200.advantage import launch_raw
@@ -37,7 +37,7 @@ def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=
     if stages is not None:
         os.environ["PUFF_ADV_STAGES"] = str(stages)
     try:
-        launch_raw(*dev, adv, *hyper, seg_abs_sum=abs_sum, variant=variant)
+        launch_raw(*dev, adv, *hyper, seg_abs_sum=abs_sum, variant=variant, flags=flags)
         kernel = cabi.last_kernel()
         torch.cuda.synchronize()
     finally:
@@ -301,3 +301,33 @@ def test_non_binary_dones_are_used_arithmetically():
     for force in ("tma2d", "bulk1d", "generic"):
         got, _, _ = run_gpu([v, r, d, w], wl.hyper(), "serial", force)
         assert bits_equal(got, want), (force, first_mismatch(got, want))
+
+
+@pytest.mark.parametrize("force", ["tma2d", "bulk1d", "scan", "generic"])
+def test_zero_last_column_flag(force):
+    """PUFF_FLAG_ZERO_LAST_COLUMN: the op owns the output and writes column H-1 = 0,
+    i.e. it reproduces the reference called on a zero-filled buffer (pufferl.py:353)
+    even when the buffer held garbage."""
+    from pufferlib_b200 import cabi
+    for S, H in ((70, 64), (33, 36), (5, 1), (9, 2), (300, 91), (64, 256), (20, 1024)):
+        if not applicable(force, H):
+            continue
+        wl = Workload("zl", S, H, seed=300 + H)
+        inputs = [t.numpy() for t in make_inputs(wl)]
+        variant = "scan" if force == "scan" else "serial"
+        got, _, _ = run_gpu(inputs, wl.hyper(), variant, force, flags=cabi.FLAG_ZERO_LAST_COLUMN)
+        want = oracle_advantage(inputs, wl.hyper(), sentinel=0.0)
+        assert np.all(got[:, -1] == 0.0), (S, H)
+        if force == "scan":
+            assert within_scan_tolerance(got, want), (S, H)
+        else:
+            assert bits_equal(got, want), f"S={S} H={H}: {first_mismatch(got, want)}"
+
+
+def test_large_config_zero_last_column():
+    from pufferlib_b200 import cabi
+    wl = WORKLOADS["cfg2"].with_segments(40000)
+    inputs = [t.numpy() for t in make_inputs(wl)]
+    got, abs_sum, kernel = run_gpu(inputs, wl.hyper(), "serial", epilogue=True, flags=cabi.FLAG_ZERO_LAST_COLUMN)
+    want = oracle_advantage(inputs, wl.hyper(), sentinel=0.0)
+    assert kernel == "tma2d" and bits_equal(got, want), first_mismatch(got, want)

@@ -92,6 +92,25 @@ def test_op_empty_and_degenerate_shapes():
     assert torch.all(s == 0)
 
 
+def test_fill_op_needs_no_zeroed_buffer():
+    import pufferlib_b200
+    wl = WORKLOADS["cfg1"]
+    host = make_inputs(wl)
+    dev = [t.cuda() for t in host]
+    garbage = torch.full_like(dev[0], float("nan"))
+    abs_sum = torch.empty(wl.segments, device="cuda")
+    out = pufferlib_b200.compute_puff_advantage_fill(*dev, *wl.hyper(), advantages=garbage, seg_abs_sum=abs_sum)
+    assert out is garbage
+    want = oracle_advantage([t.numpy() for t in host], wl.hyper(), sentinel=0.0)
+    assert bits_equal(out.cpu().numpy(), want)
+    fresh = pufferlib_b200.compute_puff_advantage_fill(*dev, *wl.hyper())
+    assert bits_equal(fresh.cpu().numpy(), want)
+    # identical to the reference sequence zeros -> op
+    zeros = torch.zeros_like(dev[0])
+    pufferlib_b200.compute_puff_advantage(*dev, zeros, *wl.hyper())
+    assert torch.equal(zeros, fresh)
+
+
 def test_meta_kernel_traces():
     from pufferlib_b200 import _C  # noqa: F401
     t = [torch.empty(8, 16, device="meta") for _ in range(5)]
