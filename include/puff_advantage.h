@@ -140,6 +140,32 @@ int puff_priorities_sm100_probs(const float* weights, const double* total_w,
                                 void* cuda_stream);
 
 /*
+ * Minibatch gather and advantage normalisation, on DEVICE buffers, asynchronous
+ * on `cuda_stream`.  Replaces the eager torch sequence of pufferl.py:363,
+ * 373-375 and 408-409 for the sampled segment indices idx[mb_segments]:
+ *     mb_prio     = (num_segments * prio_probs[idx]) ** -anneal_beta   [mb_segments]
+ *     mb_values   = values[idx]                                        [mb_segments, horizon]
+ *     mb_returns  = advantages[idx] + mb_values
+ *     mb_adv_raw  = advantages[idx]
+ *     mb_adv_norm = mb_prio[:, None] * (mb_adv_raw - mean) / (std + 1e-8)
+ * with mean and the unbiased std taken over all gathered elements (fp64
+ * accumulation through `scratch`, fixed order).  idx is int64 on the device; an
+ * index outside [0, num_segments) yields zero rows and raises the flag that
+ * puff_minibatch_sm100_bad_index() returns (and clears) after synchronising.
+ * scratch: at least puff_minibatch_sm100_scratch_bytes(mb_segments) bytes,
+ * 8-byte aligned, caller-owned.
+ */
+size_t puff_minibatch_sm100_scratch_bytes(long long mb_segments);
+int puff_minibatch_sm100_gather(const float* advantages, const float* values,
+                                const float* prio_probs, const long long* idx,
+                                float* mb_values, float* mb_returns, float* mb_adv_raw,
+                                float* mb_adv_norm, float* mb_prio, float anneal_beta,
+                                long long num_segments, long long horizon,
+                                long long mb_segments, void* scratch, size_t scratch_bytes,
+                                void* cuda_stream);
+int puff_minibatch_sm100_bad_index(void);
+
+/*
  * puff_priorities_sm100_weights for callers that cannot supply scratch.
  * (No counterpart in the reference, which allocates freely through torch.)
  *

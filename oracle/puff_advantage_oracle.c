@@ -101,3 +101,42 @@ double puff_oracle_priorities(const double *abs_sum, double *weights,
             probs[s] = (weights[s] + 1e-6) / denom;
     return local;
 }
+
+/* Minibatch gather and advantage normalisation of pufferl.py:363, 373-375,
+ * 408-409 in double:
+ *   mb_prio = (num_segments * prio_probs[idx]) ** -beta
+ *   mb_values = values[idx]; mb_returns = advantages[idx] + mb_values
+ *   adv_norm = mb_prio * (adv - mean(adv)) / (std(adv) + 1e-8),  unbiased std
+ * over all gathered elements (torch.std default). */
+void puff_oracle_minibatch(const float *advantages, const float *values,
+                           const double *prio_probs, const int64_t *idx,
+                           double *mb_values, double *mb_returns,
+                           double *mb_adv_norm, double *mb_prio, double beta,
+                           int64_t num_segments, int64_t horizon,
+                           int64_t mb_segments)
+{
+    const double n = (double)mb_segments * (double)horizon;
+    double sum = 0.0;
+    for (int64_t m = 0; m < mb_segments; m++)
+        for (int64_t t = 0; t < horizon; t++)
+            sum += (double)advantages[idx[m] * horizon + t];
+    const double mean = sum / n;
+    double ss = 0.0;
+    for (int64_t m = 0; m < mb_segments; m++)
+        for (int64_t t = 0; t < horizon; t++) {
+            const double d = (double)advantages[idx[m] * horizon + t] - mean;
+            ss += d * d;
+        }
+    const double std = sqrt(ss / (n - 1.0));
+    for (int64_t m = 0; m < mb_segments; m++) {
+        const double prio = pow((double)num_segments * prio_probs[idx[m]], -beta);
+        mb_prio[m] = prio;
+        for (int64_t t = 0; t < horizon; t++) {
+            const double a = (double)advantages[idx[m] * horizon + t];
+            const double v = (double)values[idx[m] * horizon + t];
+            mb_values[m * horizon + t] = v;
+            mb_returns[m * horizon + t] = a + v;
+            mb_adv_norm[m * horizon + t] = prio * (a - mean) / (std + 1e-8);
+        }
+    }
+}

@@ -52,6 +52,10 @@ def _load():
         lib.puff_oracle_abs_sum.restype = None
         lib.puff_oracle_priorities.argtypes = [_f64p, _f64p, _f64p, ctypes.c_double, ctypes.c_double, ctypes.c_int64]
         lib.puff_oracle_priorities.restype = ctypes.c_double
+        _i64p = ctypes.POINTER(ctypes.c_int64)
+        lib.puff_oracle_minibatch.argtypes = [_f32p, _f32p, _f64p, _i64p, _f64p, _f64p, _f64p, _f64p,
+                                              ctypes.c_double, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64]
+        lib.puff_oracle_minibatch.restype = None
         _lib = lib
     return _lib
 
@@ -100,6 +104,22 @@ def priorities(abs_sums, alpha, total_w=None):
         a.ctypes.data_as(_f64p), w.ctypes.data_as(_f64p), p.ctypes.data_as(_f64p),
         float(alpha), -1.0 if total_w is None else float(total_w), a.shape[0])
     return w, p, local
+
+
+def minibatch(advantages, values, prio_probs, idx, beta):
+    """float64 (mb_values, mb_returns, mb_adv_norm, mb_prio) of pufferl.py:363,
+    373-375, 408-409 for int64 segment indices `idx`."""
+    lib = _load()
+    adv, pa = _as_f32(advantages)
+    val, pv = _as_f32(values)
+    probs = np.ascontiguousarray(prio_probs, dtype=np.float64)
+    ix = np.ascontiguousarray(idx, dtype=np.int64)
+    S, H = adv.shape
+    M = ix.shape[0]
+    out = [np.empty((M, H), dtype=np.float64) for _ in range(3)] + [np.empty(M, dtype=np.float64)]
+    lib.puff_oracle_minibatch(pa, pv, probs.ctypes.data_as(_f64p), ix.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)),
+                              *[o.ctypes.data_as(_f64p) for o in out], float(beta), S, H, M)
+    return tuple(out)
 
 
 def load_reference(cuda=False):

@@ -12,6 +12,7 @@ from .advantage import (  # noqa: F401
     compute_puff_advantage_fill,
     compute_puff_advantage_host,
     compute_puff_advantage_prio,
+    minibatch_gather,
     prioritized_sample_probs,
     priority_probs,
     priority_weights,

@@ -69,6 +69,17 @@ def priority_probs(weights, total):
     return _ops().puff_priority_probs(weights, total)
 
 
+def minibatch_gather(advantages, values, prio_probs, idx, anneal_beta):
+    """What the trainer computes for the sampled segments `idx` (int64, CUDA)
+    right after `torch.multinomial` (pufferl.py:363, 373-375, 408-409), in two
+    launches.  Returns (mb_values, mb_returns, mb_advantages, adv, mb_prio):
+    values[idx], advantages[idx] + values[idx], advantages[idx], the
+    priority-weighted normalised advantages
+    mb_prio * (a - a.mean()) / (a.std() + 1e-8), and
+    mb_prio = (segments * prio_probs[idx, None]) ** -anneal_beta."""
+    return _ops().puff_minibatch_gather(advantages, values, prio_probs, idx, anneal_beta)
+
+
 def prioritized_sample_probs(values, rewards, terminals, ratio, advantages,
                              gamma, gae_lambda, vtrace_rho_clip, vtrace_c_clip, prio_alpha,
                              process_group=None):

@@ -186,6 +186,47 @@ torch::Tensor puff_priority_probs_cuda(torch::Tensor weights, torch::Tensor tota
     return probs;
 }
 
+// pufferl.py:363, 373-375, 408-409 for sampled segment indices.
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor>
+puff_minibatch_gather_cuda(torch::Tensor advantages, torch::Tensor values, torch::Tensor prio_probs,
+                           torch::Tensor idx, double anneal_beta)
+{
+    TORCH_CHECK(advantages.is_cuda(), "All tensors must be on GPU");
+    TORCH_CHECK(advantages.dim() == 2 && values.dim() == 2 && advantages.sizes() == values.sizes(),
+                "advantages and values must be 2D of one shape");
+    TORCH_CHECK(prio_probs.dim() == 1 && prio_probs.size(0) == advantages.size(0), "prio_probs must be [segments]");
+    TORCH_CHECK(idx.dim() == 1 && idx.dtype() == torch::kInt64, "idx must be a 1D int64 tensor");
+    for (const torch::Tensor& t : {advantages, values, prio_probs}) {
+        TORCH_CHECK(t.dtype() == torch::kFloat32, "All tensors must be float32");
+        TORCH_CHECK(t.is_contiguous(), "All tensors must be contiguous");
+        TORCH_CHECK(t.device() == advantages.device(), "All tensors must be on same device");
+    }
+    TORCH_CHECK(idx.is_contiguous() && idx.device() == advantages.device(), "idx must be contiguous on the same device");
+    const int64_t S = advantages.size(0), H = advantages.size(1), M = idx.size(0);
+    int rc;
+    torch::Tensor mb_values, mb_returns, mb_raw, mb_norm, mb_prio;
+    {
+        const c10::cuda::CUDAGuard guard(advantages.device());
+        const auto opts = advantages.options();
+        mb_values = torch::empty({M, H}, opts);
+        mb_returns = torch::empty({M, H}, opts);
+        mb_raw = torch::empty({M, H}, opts);
+        mb_norm = torch::empty({M, H}, opts);
+        mb_prio = torch::empty({M, 1}, opts);
+        const size_t sbytes = puff_minibatch_sm100_scratch_bytes(M);
+        auto scratch = torch::empty({static_cast<int64_t>((sbytes + 7) / 8)}, opts.dtype(torch::kFloat64));
+        rc = puff_minibatch_sm100_gather(advantages.data_ptr<float>(), values.data_ptr<float>(),
+                                         prio_probs.data_ptr<float>(),
+                                         reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()),
+                                         mb_values.data_ptr<float>(), mb_returns.data_ptr<float>(),
+                                         mb_raw.data_ptr<float>(), mb_norm.data_ptr<float>(), mb_prio.data_ptr<float>(),
+                                         static_cast<float>(anneal_beta), S, H, M, scratch.data_ptr<double>(), sbytes,
+                                         at::cuda::getCurrentCUDAStream().stream());
+    }
+    check_rc(rc, "puff_minibatch_gather");
+    return {mb_values, mb_returns, mb_raw, mb_norm, mb_prio};
+}
+
 // Shape-only kernels so the ops can be traced (torch.compile / fake tensors).
 void compute_puff_advantage_meta(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor,
                                  double, double, double, double) {}
@@ -200,6 +241,7 @@ TORCH_LIBRARY(pufferlib, m)
     m.def("compute_puff_advantage_fill(Tensor values, Tensor rewards, Tensor dones, Tensor importance, Tensor(a!) advantages, Tensor(b!)? seg_abs_sum, float gamma, float lambda, float rho_clip, float c_clip) -> ()");
     m.def("puff_priority_weights(Tensor seg_abs_sum, float alpha) -> (Tensor, Tensor)");
     m.def("puff_priority_probs(Tensor weights, Tensor total_w) -> Tensor");
+    m.def("puff_minibatch_gather(Tensor advantages, Tensor values, Tensor prio_probs, Tensor idx, float anneal_beta) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(pufferlib, CUDA, m)
@@ -209,6 +251,7 @@ TORCH_LIBRARY_IMPL(pufferlib, CUDA, m)
     m.impl("compute_puff_advantage_fill", &compute_puff_advantage_fill_cuda);
     m.impl("puff_priority_weights", &puff_priority_weights_cuda);
     m.impl("puff_priority_probs", &puff_priority_probs_cuda);
+    m.impl("puff_minibatch_gather", &puff_minibatch_gather_cuda);
 }
 
 TORCH_LIBRARY_IMPL(pufferlib, Meta, m)

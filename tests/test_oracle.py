@@ -95,3 +95,24 @@ def test_shard_rows_cover():
             spans = [shard_rows(S, r, W) for r in range(W)]
             assert spans[0][0] == 0 and spans[-1][1] == S
             assert all(spans[i][1] == spans[i + 1][0] for i in range(W - 1))
+
+
+def test_minibatch_oracle_matches_torch_sequence():
+    """The fp64 restatement of pufferl.py:363, 373-375, 408-409 against the
+    same lines evaluated with torch in float64."""
+    from oracle import puff_oracle
+    g = torch.Generator().manual_seed(4)
+    S, H, M, beta = 200, 48, 37, 0.4
+    adv = torch.randn(S, H, generator=g)
+    val = torch.randn(S, H, generator=g)
+    probs = torch.rand(S, generator=g).double() + 0.01
+    probs = probs / probs.sum()
+    idx = torch.multinomial(probs, M, generator=g)
+    o_v, o_r, o_n, o_p = puff_oracle.minibatch(adv.numpy(), val.numpy(), probs.numpy(), idx.numpy(), beta)
+    a64, v64 = adv.double(), val.double()
+    mb_prio = (S * probs[idx, None]) ** -beta
+    e = a64[idx]
+    e = mb_prio * (e - e.mean()) / (e.std() + 1e-8)
+    np.testing.assert_allclose(o_n, e.numpy(), rtol=1e-12, atol=1e-14)
+    np.testing.assert_allclose(o_r, (a64[idx] + v64[idx]).numpy(), rtol=0, atol=0)
+    np.testing.assert_allclose(o_p, mb_prio.numpy()[:, 0], rtol=1e-13)

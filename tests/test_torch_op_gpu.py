@@ -190,3 +190,50 @@ def test_standalone_nvcc_harness(tmp_path):
     out = subprocess.run([exe], capture_output=True, text=True)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "OK" in out.stdout
+
+
+@pytest.mark.parametrize("S,H,M", [(8192, 64, 512), (1000, 91, 333), (64, 256, 64), (50, 1, 7), (300, 128, 1)])
+def test_minibatch_gather_matches_oracle_and_torch(S, H, M):
+    """pufferl.py:363, 373-375, 408-409 fused: against the fp64 oracle and the
+    eager torch sequence on the same device."""
+    import pufferlib_b200
+    from oracle import puff_oracle
+    g = torch.Generator().manual_seed(S + H)
+    adv = torch.randn(S, H, generator=g)
+    adv[:, -1] = 0
+    val = torch.randn(S, H, generator=g)
+    probs = torch.rand(S, generator=g) + 0.01
+    probs = probs / probs.sum()
+    idx = torch.multinomial(probs, M, generator=g)
+    beta = 0.35
+    d_adv, d_val, d_probs, d_idx = adv.cuda(), val.cuda(), probs.cuda(), idx.cuda()
+    mv, mr, ma, an, mp = pufferlib_b200.minibatch_gather(d_adv, d_val, d_probs, d_idx, beta)
+    assert mp.shape == (M, 1)
+    # gathers are exact
+    assert torch.equal(mv, d_val[d_idx]) and torch.equal(ma, d_adv[d_idx])
+    assert torch.equal(mr, d_adv[d_idx] + d_val[d_idx])
+    o_v, o_r, o_n, o_p = puff_oracle.minibatch(adv.numpy(), val.numpy(), probs.double().numpy(), idx.numpy(), beta)
+    np.testing.assert_allclose(mp.cpu().numpy()[:, 0], o_p, rtol=1e-5)
+    if M * H > 1:
+        np.testing.assert_allclose(an.cpu().numpy(), o_n, rtol=1e-5, atol=2e-6)
+        e_prio = (S * d_probs[d_idx, None]) ** -beta
+        e_adv = ma
+        e_adv = e_prio * (e_adv - e_adv.mean()) / (e_adv.std() + 1e-8)
+        np.testing.assert_allclose(an.cpu().numpy(), e_adv.cpu().numpy(), rtol=1e-4, atol=1e-5)
+    else:
+        assert torch.isnan(an).all()          # std of one element is NaN in the reference as well
+    from pufferlib_b200 import cabi
+    assert cabi.load().puff_minibatch_sm100_bad_index() == 0
+
+
+def test_minibatch_gather_flags_bad_indices():
+    import pufferlib_b200
+    from pufferlib_b200 import cabi
+    adv = torch.randn(16, 32, device="cuda")
+    val = torch.randn(16, 32, device="cuda")
+    probs = torch.full((16,), 1 / 16, device="cuda")
+    idx = torch.tensor([0, 3, 99, -1], device="cuda")
+    mv, mr, ma, an, mp = pufferlib_b200.minibatch_gather(adv, val, probs, idx, 0.5)
+    assert cabi.load().puff_minibatch_sm100_bad_index() == 1
+    assert cabi.load().puff_minibatch_sm100_bad_index() == 0      # cleared by the read
+    assert torch.equal(mv[:2], val[idx[:2]]) and torch.all(mv[2:] == 0)
