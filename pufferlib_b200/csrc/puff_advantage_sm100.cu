@@ -511,20 +511,21 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
 // split by dependency instead:
 //   warp 0      producer: waits for a free stage, issues the four TMA loads
 //   warps 2..5  terms:    128 threads, 8 columns of one row each, read the raw
-//                         boxes and write (delta, gamma*lambda*c, nn) for every
-//                         step into a terms buffer (same swizzled layout);
-//                         columns without a step get delta = gc = 0
+//                         boxes and write delta and k = (gamma*lambda*c)*nn of
+//                         every step into a terms buffer (same swizzled layout);
+//                         columns without a step get delta = k = 0
 //   warp 1      chain:    lane r walks row r's 32 steps from the terms buffer,
-//                         A = delta + (gc*nn)*A (or the literal order when the
-//                         terms warps flagged a non-binary nn or A nears the
-//                         overflow range), stores the advantages by TMA
+//                         A = delta + k*A, stores the advantages by TMA.  When the
+//                         terms warps flagged a non-binary nn, or A nears the
+//                         overflow range, it redoes the chunk in the reference's
+//                         literal order straight from global memory (rare, slow)
 // Rings: NST raw stages (full: TMA -> terms, sfree: terms -> producer) and NT
 // terms buffers (tfull: terms -> chain, tfree: chain -> terms).
 constexpr int kWsTermWarps = 4;
 constexpr int kWsThreads = 32 * (2 + kWsTermWarps);
-constexpr int kTermBytes = 4 * kBoxBytes;   // delta | k = gc*nn | gc | nn
+constexpr int kTermBytes = 2 * kBoxBytes;   // delta | k = (gamma*lambda*c)*nn
 
-constexpr int kWsOutSlots = 4;   // output boxes in flight behind the TMA stores
+constexpr int kWsOutSlots = 2;   // output boxes in flight behind the TMA stores
 template <int NST, int NT>
 constexpr int tma2d_ws_smem_bytes()
 {
@@ -572,8 +573,11 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                          const __grid_constant__ CUtensorMap tm_d,
                          const __grid_constant__ CUtensorMap tm_w,
                          const __grid_constant__ CUtensorMap tm_a,
+                         const float* __restrict__ raw_v, const float* __restrict__ raw_r,
+                         const float* __restrict__ raw_d, const float* __restrict__ raw_w,
                          const float* adv_in, float* __restrict__ seg_abs_sum, float gamma, float lambda,
-                         float rho_clip, float c_clip, long long num_segments, int horizon, int num_tiles)
+                         float rho_clip, float c_clip, long long num_segments, int horizon, int num_tiles,
+                         int group)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -617,28 +621,39 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             prefetch_tensormap(&tm_r);
             prefetch_tensormap(&tm_d);
             prefetch_tensormap(&tm_w);
+            // Loads are issued in groups of `group` consecutive chunks (NST % group == 0):
+            // the producer waits until all their stages are free and then issues them back
+            // to back, so that DRAM sees group*128 contiguous bytes of every row at once.
             int k = 0, c = nchunks - 1, s = 0, round = 0;
-            for (int i = 0; i < total; ++i) {
-                if (round > 0 && !mbar_wait_thread(bar_sfree + 8 * s, static_cast<uint32_t>(round - 1) & 1u)) {
-                    failed = true;
-                    break;
+            for (int i = 0; i < total && !failed; i += group) {
+                const int n = total - i < group ? total - i : group;
+                if (round > 0) {
+                    for (int j = 0; j < n; ++j) {
+                        if (!mbar_wait_thread(bar_sfree + 8 * (s + j), static_cast<uint32_t>(round - 1) & 1u)) {
+                            failed = true;
+                            break;
+                        }
+                    }
+                    if (failed) break;
                 }
-                const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
-                const uint32_t st = base + s * kStageBytes;
-                const uint32_t bar = bar_full + 8 * s;
-                const int x = c * kChunkCols, y = tile * kTileRows;
-                mbar_expect_tx(bar, kStageBytes);
-                tma_load_2d(st + 0 * kBoxBytes, &tm_v, x, y, bar);
-                tma_load_2d(st + 1 * kBoxBytes, &tm_r, x, y, bar);
-                tma_load_2d(st + 2 * kBoxBytes, &tm_d, x, y, bar);
-                tma_load_2d(st + 3 * kBoxBytes, &tm_w, x, y, bar);
-                if (--c < 0) {
-                    c = nchunks - 1;
-                    ++k;
-                }
-                if (++s == NST) {
-                    s = 0;
-                    ++round;
+                for (int j = 0; j < n; ++j) {
+                    const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+                    const uint32_t st = base + s * kStageBytes;
+                    const uint32_t bar = bar_full + 8 * s;
+                    const int x = c * kChunkCols, y = tile * kTileRows;
+                    mbar_expect_tx(bar, kStageBytes);
+                    tma_load_2d(st + 0 * kBoxBytes, &tm_v, x, y, bar);
+                    tma_load_2d(st + 1 * kBoxBytes, &tm_r, x, y, bar);
+                    tma_load_2d(st + 2 * kBoxBytes, &tm_d, x, y, bar);
+                    tma_load_2d(st + 3 * kBoxBytes, &tm_w, x, y, bar);
+                    if (--c < 0) {
+                        c = nchunks - 1;
+                        ++k;
+                    }
+                    if (++s == NST) {
+                        s = 0;
+                        ++round;
+                    }
                 }
             }
             if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
@@ -711,10 +726,6 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             sts128(tb + 0 * kBoxBytes + off1, make_float4(dl[4], dl[5], dl[6], dl[7]));
             sts128(tb + 1 * kBoxBytes + off0, make_float4(kk[0], kk[1], kk[2], kk[3]));
             sts128(tb + 1 * kBoxBytes + off1, make_float4(kk[4], kk[5], kk[6], kk[7]));
-            sts128(tb + 2 * kBoxBytes + off0, make_float4(gc[0], gc[1], gc[2], gc[3]));
-            sts128(tb + 2 * kBoxBytes + off1, make_float4(gc[4], gc[5], gc[6], gc[7]));
-            sts128(tb + 3 * kBoxBytes + off0, make_float4(nn[0], nn[1], nn[2], nn[3]));
-            sts128(tb + 3 * kBoxBytes + off1, make_float4(nn[4], nn[5], nn[6], nn[7]));
             if ((nonbin << 1) != 0u) sts32u(flag_base + 4 * b, 1u);
             __syncwarp();
             if (lane == 0) {
@@ -763,6 +774,13 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 kk[4 * u] = y.x; kk[4 * u + 1] = y.y; kk[4 * u + 2] = y.z; kk[4 * u + 3] = y.w;
             }
             const uint32_t flag = lds32u(flag_base + 4 * b);
+            // the terms buffer is free as soon as every lane holds its values
+            __syncwarp();
+            if (lane == 0) {
+                if (flag != 0u) sts32u(flag_base + 4 * b, 0u);
+                mbar_arrive(bar_tfree + 8 * b);
+            }
+            const int cbase = c * kChunkCols;
             const float a_in = a_run;
             bool literal = flag != 0u;
             float abs_chunk = 0.0f;
@@ -775,33 +793,24 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 abs_chunk = abs_tree32(out);
                 literal = __any_sync(0xffffffffu, !(__fadd_rn(fabsf(a_in), abs_chunk) <= 1e30f));
             }
-            if (literal) {   // rare: the reference's literal order, from gc and nn
+            if (literal) {   // rare: the reference's literal order, operands straight from global memory
                 a_run = a_in;
+                const long long row = static_cast<long long>(tile) * kTileRows + lane;
+                const bool in_rows = row < num_segments;
+                const long long ro = (in_rows ? row : 0) * horizon;
 #pragma unroll
-                for (int u = 7; u >= 0; --u) {
-                    const uint32_t off = row_off + ((static_cast<uint32_t>(u) ^ sw) << 4);
-                    const float4 y = lds128(tb + 2 * kBoxBytes + off);
-                    const float4 z = lds128(tb + 3 * kBoxBytes + off);
-                    a_run = __fadd_rn(dl[4 * u + 3], __fmul_rn(__fmul_rn(y.w, a_run), z.w));
-                    out[4 * u + 3] = a_run;
-                    a_run = __fadd_rn(dl[4 * u + 2], __fmul_rn(__fmul_rn(y.z, a_run), z.z));
-                    out[4 * u + 2] = a_run;
-                    a_run = __fadd_rn(dl[4 * u + 1], __fmul_rn(__fmul_rn(y.y, a_run), z.y));
-                    out[4 * u + 1] = a_run;
-                    a_run = __fadd_rn(dl[4 * u], __fmul_rn(__fmul_rn(y.x, a_run), z.x));
-                    out[4 * u] = a_run;
+                for (int j = 31; j >= 0; --j) {
+                    const int t = cbase + j;
+                    if (in_rows && t < horizon - 1)
+                        a_run = adv_step(__ldg(raw_v + ro + t), __ldg(raw_w + ro + t), __ldg(raw_v + ro + t + 1),
+                                         __ldg(raw_r + ro + t + 1), __ldg(raw_d + ro + t + 1), a_run, gamma, gl,
+                                         rho_clip, c_clip);
+                    out[j] = a_run;
                 }
                 abs_chunk = abs_tree32(out);
             }
-            // the terms buffer is free once every lane has its values (and the rare path is done)
-            __syncwarp();
-            if (lane == 0) {
-                if (flag != 0u) sts32u(flag_base + 4 * b, 0u);
-                mbar_arrive(bar_tfree + 8 * b);
-            }
             if (EPI) abs_run = __fadd_rn(abs_run, abs_chunk);
             const uint32_t ob = out_base + oslot * kBoxBytes;
-            const int cbase = c * kChunkCols;
             if (lane == 0) bulk_wait_read<kWsOutSlots - 1>();   // the store that last used this box has read it
             __syncwarp();
 #pragma unroll
@@ -1331,14 +1340,10 @@ static const DeviceInfo* device_info(int* code)
                 set_tma2d_attrs<6>();
                 set_tma2d_attrs<8>();
                 set_tma2d_attrs<12>();
+                set_tma2d_ws_attrs<2, 2>();
                 set_tma2d_ws_attrs<3, 2>();
                 set_tma2d_ws_attrs<4, 2>();
-                set_tma2d_ws_attrs<5, 2>();
                 set_tma2d_ws_attrs<6, 2>();
-                set_tma2d_ws_attrs<8, 2>();
-                set_tma2d_ws_attrs<10, 2>();
-                set_tma2d_ws_attrs<4, 3>();
-                set_tma2d_ws_attrs<8, 3>();
                 cudaFuncSetAttribute(puff_adv_bulk1d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem_optin);
                 d.err = cudaGetLastError();
             }
@@ -1422,14 +1427,16 @@ template <int NST, int NT>
 static cudaError_t launch_tma2d_ws(const MapSet& m, const float* adv_in, float* seg_abs_sum, float gamma, float lambda, float rho_clip,
                                    float c_clip, long long rows, int horizon, int grid, int tiles, cudaStream_t st)
 {
+    int group = env_int("PUFF_ADV_GROUP", NST % 2 == 0 ? 2 : 1);
+    if (group < 1 || NST % group != 0) group = 1;
     if (seg_abs_sum != nullptr)
         puff_adv_tma2d_ws_kernel<NST, NT, true><<<grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], adv_in, seg_abs_sum, gamma, lambda, rho_clip, c_clip,
-            rows, horizon, tiles);
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[0], m.ptr[1], m.ptr[2], m.ptr[3], adv_in, seg_abs_sum, gamma, lambda, rho_clip, c_clip,
+            rows, horizon, tiles, group);
     else
         puff_adv_tma2d_ws_kernel<NST, NT, false><<<grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], adv_in, nullptr, gamma, lambda, rho_clip, c_clip,
-            rows, horizon, tiles);
+            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[0], m.ptr[1], m.ptr[2], m.ptr[3], adv_in, nullptr, gamma, lambda, rho_clip, c_clip,
+            rows, horizon, tiles, group);
     return cudaGetLastError();
 }
 
@@ -1588,28 +1595,26 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             }
             const long long tiles = (rows + kTileRows - 1) / kTileRows;
             float* abs_p = seg_abs_sum != nullptr ? seg_abs_sum + r0 : nullptr;
-            // Large buffers: the warp-specialised kernel (three stages, two terms buffers,
-            // two CTAs per SM measured best on 131072 x 256).  Buffers of only a few tiles
-            // per SM finish sooner on the single-warp kernel, whose pipeline has fewer hops.
-            // PUFF_ADV_WS: 0 = single-warp, 10*NST + NT = warp-specialised with that shape.
-            const int ws = env_int("PUFF_ADV_WS", tiles >= 4LL * dev->sm_count ? 32 : 0);
+            // Large buffers: the warp-specialised kernel.  Measured on 131072 x 256: four raw
+            // stages whose loads are issued two chunks at a time, two terms buffers, two CTAs
+            // per SM (more CTAs per SM lowered the achieved DRAM rate).  Buffers of only a few
+            // tiles per SM finish sooner on the single-warp kernel, whose pipeline has fewer hops.
+            // PUFF_ADV_WS: 0 = single-warp, N = warp-specialised with N raw stages (2, 3, 4, 6).
+            const int ws = env_int("PUFF_ADV_WS", tiles >= 4LL * dev->sm_count ? 4 : 0);
             if (ws != 0) {
-                int wnst = ws >= 10 ? ws / 10 : 3, wnt = ws >= 10 ? ws % 10 : 2;
-                const int smem = wnt == 3 ? (wnst >= 8 ? tma2d_ws_smem_bytes<8, 3>() : tma2d_ws_smem_bytes<4, 3>())
-                                          : (wnst * kStageBytes + 2 * kTermBytes + kWsOutSlots * kBoxBytes + 2048);
+                const int wnst = ws <= 2 ? 2 : ws == 3 ? 3 : ws <= 5 ? 4 : 6;
+                const int smem = wnst * kStageBytes + 2 * kTermBytes + kWsOutSlots * kBoxBytes + 2048;
                 int per_sm = (dev->max_smem_optin + 1024) / (smem + 1024);
-                { const int o = env_int("PUFF_ADV_CTAS_PER_SM", 0); if (o > 0 && o < per_sm) per_sm = o; }
+                if (per_sm > 2) per_sm = 2;
+                { const int o = env_int("PUFF_ADV_CTAS_PER_SM", 0); if (o > 0) per_sm = o < 3 ? o : 3; }
                 if (per_sm < 1) per_sm = 1;
                 const long long mg = static_cast<long long>(dev->sm_count) * per_sm;
                 const int grid = static_cast<int>(tiles < mg ? tiles : mg);
 #define PUFF_WS_CASE(A, B) err = launch_tma2d_ws<A, B>(cache, zero_last ? nullptr : p[4], abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st)
-                if (wnt == 3) { if (wnst >= 8) PUFF_WS_CASE(8, 3); else PUFF_WS_CASE(4, 3); }
-                else if (wnst <= 3) PUFF_WS_CASE(3, 2);
+                if (wnst == 2) PUFF_WS_CASE(2, 2);
+                else if (wnst == 3) PUFF_WS_CASE(3, 2);
                 else if (wnst == 4) PUFF_WS_CASE(4, 2);
-                else if (wnst == 5) PUFF_WS_CASE(5, 2);
-                else if (wnst <= 6) PUFF_WS_CASE(6, 2);
-                else if (wnst <= 8) PUFF_WS_CASE(8, 2);
-                else PUFF_WS_CASE(10, 2);
+                else PUFF_WS_CASE(6, 2);
 #undef PUFF_WS_CASE
                 g_launch_count.fetch_add(1, std::memory_order_relaxed);
                 continue;
