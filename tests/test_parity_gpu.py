@@ -18,14 +18,14 @@ FORCE = {"tma2d": 1, "bulk1d": 2, "scan": 3, "generic": 4}
 
 @pytest.fixture(autouse=True)
 def _clear_force():
-    os.environ.pop("PUFF_ADV_FORCE_KERNEL", None)
-    os.environ.pop("PUFF_ADV_STAGES", None)
+    for k in ("PUFF_ADV_FORCE_KERNEL", "PUFF_ADV_STAGES", "PUFF_ADV_WS"):
+        os.environ.pop(k, None)
     yield
-    os.environ.pop("PUFF_ADV_FORCE_KERNEL", None)
-    os.environ.pop("PUFF_ADV_STAGES", None)
+    for k in ("PUFF_ADV_FORCE_KERNEL", "PUFF_ADV_STAGES", "PUFF_ADV_WS"):
+        os.environ.pop(k, None)
 
 
-def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=SENTINEL, stages=None, flags=0):
+def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=SENTINEL, stages=None, flags=0, ws=None):
     """Launch through the C ABI; returns (advantages, abs_sum or None, kernel name)."""
     from pufferlib_b200 import cabi
     from pufferlib_b200.advantage import launch_raw
@@ -36,6 +36,8 @@ def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=
         os.environ["PUFF_ADV_FORCE_KERNEL"] = str(FORCE[force])
     if stages is not None:
         os.environ["PUFF_ADV_STAGES"] = str(stages)
+    if ws is not None:
+        os.environ["PUFF_ADV_WS"] = str(ws)      # 0: single-warp tma2d, N: warp-specialised with N stages
     try:
         launch_raw(*dev, adv, *hyper, seg_abs_sum=abs_sum, variant=variant, flags=flags)
         kernel = cabi.last_kernel()
@@ -43,6 +45,7 @@ def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=
     finally:
         os.environ.pop("PUFF_ADV_FORCE_KERNEL", None)
         os.environ.pop("PUFF_ADV_STAGES", None)
+        os.environ.pop("PUFF_ADV_WS", None)
     assert cabi.device_status() == 0
     return adv.cpu().numpy(), None if abs_sum is None else abs_sum.cpu().numpy(), kernel
 
@@ -331,3 +334,62 @@ def test_large_config_zero_last_column():
     got, abs_sum, kernel = run_gpu(inputs, wl.hyper(), "serial", epilogue=True, flags=cabi.FLAG_ZERO_LAST_COLUMN)
     want = oracle_advantage(inputs, wl.hyper(), sentinel=0.0)
     assert kernel == "tma2d" and bits_equal(got, want), first_mismatch(got, want)
+
+
+# ---------------------------------------------------------------------------
+# both forms of the tma2d kernel (single-warp and warp-specialised) on the
+# cases that normally only reach one of them
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("ws", [0, 2, 3, 4, 6])
+def test_tma2d_forms_match_golden(golden_small, ws):
+    for name, case in golden_small.items():
+        H = case["values"].shape[1]
+        if H % 4 or H < 2:
+            continue
+        got, _, kernel = run_gpu([case[k] for k in KEYS], case["hyper"], "serial", "tma2d", ws=ws)
+        assert kernel == "tma2d"
+        assert bits_equal(got, case["advantages"]), f"{name}/ws={ws}: {first_mismatch(got, case['advantages'])}"
+
+
+@pytest.mark.parametrize("ws", [0, 4])
+def test_tma2d_forms_shape_sweep(ws):
+    seed = 500
+    for S in (1, 31, 33, 64, 70, 257):
+        for H in (4, 8, 28, 32, 36, 60, 64, 68, 96, 128, 132, 256, 260):
+            wl = Workload("ws", S, H, seed=seed, done_p=0.1)
+            seed += 1
+            inputs = [t.numpy() for t in make_inputs(wl)]
+            got, abs_sum, _ = run_gpu(inputs, wl.hyper(), "serial", "tma2d", epilogue=True, ws=ws)
+            want = oracle_advantage(inputs, wl.hyper())
+            assert bits_equal(got, want), f"S={S} H={H} ws={ws}: {first_mismatch(got, want)}"
+            exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
+            np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("ws", [0, 3, 4])
+def test_tma2d_forms_literal_paths(ws):
+    """Non-binary dones and products near overflow send a chunk down the
+    literal path: from the shared-memory stage in the single-warp form, from
+    global memory in the warp-specialised form."""
+    wl = Workload("lit", 300, 192, seed=77)
+    v, r, d, w = [t.numpy() for t in make_inputs(wl)]
+    d = np.random.default_rng(9).random(d.shape).astype(np.float32)
+    d[::2] = (d[::2] > 0.7)
+    want = oracle_advantage([v, r, d, w], wl.hyper())
+    got, _, _ = run_gpu([v, r, d, w], wl.hyper(), "serial", "tma2d", ws=ws)
+    assert bits_equal(got, want), first_mismatch(got, want)
+    # overflow of (gamma*lambda*c)*A with nn == 0 -> NaN in the reference
+    rng = np.random.default_rng(5)
+    S, H = 80, 128
+    v = rng.standard_normal((S, H)).astype(np.float32)
+    r = rng.standard_normal((S, H)).astype(np.float32)
+    d = (rng.random((S, H)) < 0.2).astype(np.float32)
+    w = np.full((S, H), 4.0, dtype=np.float32)
+    r[:, 100] = 2.5e38
+    d[:, 99] = 1.0
+    d[:, 100] = 0.0
+    hyper = (1.0, 1.0, 1.0, 4.0)
+    want = oracle_advantage([v, r, d, w], hyper)
+    assert np.isnan(want[:, 98]).all()
+    got, _, _ = run_gpu([v, r, d, w], hyper, "serial", "tma2d", ws=ws)
+    assert bits_equal(got, want), first_mismatch(got, want)
