@@ -1598,9 +1598,11 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             // Large buffers: the warp-specialised kernel.  Measured on 131072 x 256: four raw
             // stages whose loads are issued two chunks at a time, two terms buffers, two CTAs
             // per SM (more CTAs per SM lowered the achieved DRAM rate).  Buffers of only a few
-            // tiles per SM finish sooner on the single-warp kernel, whose pipeline has fewer hops.
+            // chunks per SM (8192 x 64 and smaller) finish sooner on the single-warp kernel,
+            // whose pipeline has fewer hops.
             // PUFF_ADV_WS: 0 = single-warp, N = warp-specialised with N raw stages (2, 3, 4, 6).
-            const int ws = env_int("PUFF_ADV_WS", tiles >= 4LL * dev->sm_count ? 4 : 0);
+            const long long work_items = tiles * ((horizon + kChunkCols - 1) / kChunkCols);
+            const int ws = env_int("PUFF_ADV_WS", work_items >= 8LL * dev->sm_count ? 4 : 0);
             if (ws != 0) {
                 const int wnst = ws <= 2 ? 2 : ws == 3 ? 3 : ws <= 5 ? 4 : 6;
                 const int smem = wnst * kStageBytes + 2 * kTermBytes + kWsOutSlots * kBoxBytes + 2048;
