@@ -209,6 +209,17 @@ long long puff_advantage_sm100_launch_count(void);
  * status word: 0, or PUFF_ERR_DEVICE_WAIT when a bounded wait inside a kernel
  * gave up.  Meant for tests and debugging; the launch path never calls it. */
 int puff_advantage_sm100_device_status(void);
+/* Tuning knobs for tests and sweeps (process-wide; value -1 restores the
+ * automatic choice; returns the previous value, or PUFF_ERR_VARIANT for an
+ * unknown knob).  The initial values come from the environment variables named
+ * beside each knob, read once. */
+#define PUFF_TUNE_FORCE_KERNEL  0   /* PUFF_ADV_FORCE_KERNEL: a PUFF_KERNEL_* to use whenever it applies */
+#define PUFF_TUNE_STAGES        1   /* PUFF_ADV_STAGES: ring depth of the single-warp tma2d kernel (2,3,4,6,8,12) */
+#define PUFF_TUNE_WS_STAGES     2   /* PUFF_ADV_WS: 0 = single-warp tma2d, N = warp-specialised with N stages */
+#define PUFF_TUNE_CTAS_PER_SM   3   /* PUFF_ADV_CTAS_PER_SM: cap on resident CTAs per SM of the tma2d kernels */
+#define PUFF_TUNE_LOAD_GROUP    4   /* PUFF_ADV_GROUP: chunks whose loads the warp-specialised producer issues together */
+#define PUFF_TUNE_COUNT         5
+int puff_advantage_sm100_set_tuning(int knob, int value);
 /* Library version, "major.minor". */
 const char* puff_advantage_sm100_version(void);
 

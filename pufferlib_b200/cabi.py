@@ -46,6 +46,7 @@ SIGNATURES = {
     "puff_advantage_sm100_last_kernel": (_I, []),
     "puff_advantage_sm100_launch_count": (_LL, []),
     "puff_advantage_sm100_device_status": (_I, []),
+    "puff_advantage_sm100_set_tuning": (_I, [_I, _I]),
     "puff_advantage_sm100_version": (ctypes.c_char_p, []),
 }
 
@@ -67,6 +68,20 @@ def load():
             fn.argtypes = args
         _lib = lib
     return _lib
+
+
+TUNE = {"force_kernel": 0, "stages": 1, "ws_stages": 2, "ctas_per_sm": 3, "load_group": 4}
+
+
+def set_tuning(**knobs):
+    """Set tuning knobs by name (see PUFF_TUNE_* in the header); None or -1
+    restores the automatic choice.  Returns the previous values."""
+    lib = load()
+    return {k: lib.puff_advantage_sm100_set_tuning(TUNE[k], -1 if v is None else int(v)) for k, v in knobs.items()}
+
+
+def reset_tuning():
+    set_tuning(**{k: None for k in TUNE})
 
 
 def strerror(code):

@@ -1401,11 +1401,30 @@ struct MapSet {
     CUtensorMap tm[5];
 };
 
-static int env_int(const char* name, int fallback)
+// Tuning knobs (tests, sweeps): process-wide, -1 = automatic.  Initialised once from the
+// environment (PUFF_ADV_FORCE_KERNEL, PUFF_ADV_STAGES, PUFF_ADV_WS, PUFF_ADV_CTAS_PER_SM,
+// PUFF_ADV_GROUP) and changed at run time through puff_advantage_sm100_set_tuning, so the
+// launch path itself never touches the environment.
+static std::atomic<int> g_tune[PUFF_TUNE_COUNT];
+static std::once_flag g_tune_once;
+
+static void tune_init()
 {
-    const char* s = getenv(name);
-    if (s == nullptr || *s == '\0') return fallback;
-    return atoi(s);
+    std::call_once(g_tune_once, [] {
+        static const char* const names[PUFF_TUNE_COUNT] = {"PUFF_ADV_FORCE_KERNEL", "PUFF_ADV_STAGES", "PUFF_ADV_WS",
+                                                           "PUFF_ADV_CTAS_PER_SM", "PUFF_ADV_GROUP"};
+        for (int i = 0; i < PUFF_TUNE_COUNT; ++i) {
+            const char* v = getenv(names[i]);
+            g_tune[i].store((v != nullptr && *v != '\0') ? atoi(v) : -1, std::memory_order_relaxed);
+        }
+    });
+}
+
+static int tune(int knob, int fallback)
+{
+    tune_init();
+    const int v = g_tune[knob].load(std::memory_order_relaxed);
+    return v < 0 ? fallback : v;
 }
 
 template <int NST>
@@ -1427,7 +1446,7 @@ template <int NST, int NT>
 static cudaError_t launch_tma2d_ws(const MapSet& m, const float* adv_in, float* seg_abs_sum, float gamma, float lambda, float rho_clip,
                                    float c_clip, long long rows, int horizon, int grid, int tiles, cudaStream_t st)
 {
-    int group = env_int("PUFF_ADV_GROUP", NST % 2 == 0 ? 2 : 1);
+    int group = tune(PUFF_TUNE_LOAD_GROUP, NST % 2 == 0 ? 2 : 1);
     if (group < 1 || NST % group != 0) group = 1;
     if (seg_abs_sum != nullptr)
         puff_adv_tma2d_ws_kernel<NST, NT, true><<<grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st>>>(
@@ -1556,7 +1575,7 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             kernel = serial_kernel;
     }
     {
-        const int forced = env_int("PUFF_ADV_FORCE_KERNEL", 0);   // tests: 1..4
+        const int forced = tune(PUFF_TUNE_FORCE_KERNEL, 0);   // tests: PUFF_KERNEL_*
         if (forced == PUFF_KERNEL_TMA2D && can_tma2d) kernel = forced;
         if (forced == PUFF_KERNEL_BULK1D && can_bulk1d) kernel = forced;
         if (forced == PUFF_KERNEL_SCAN && can_scan) kernel = forced;
@@ -1570,12 +1589,12 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
         static thread_local MapSet cache;
         // measured on cfg2 (131072 x 256): two CTAs per SM with a four-stage ring each
         // beat both more, shallower CTAs and one deeper CTA
-        int nst = env_int("PUFF_ADV_STAGES", 4);
+        int nst = tune(PUFF_TUNE_STAGES, 4);
         nst = nst <= 2 ? 2 : nst == 3 ? 3 : nst == 4 ? 4 : nst <= 6 ? 6 : nst <= 8 ? 8 : 12;
         const int stage_smem = nst * kStageBytes + 2 * kBoxBytes + nst * 8 + 1024;
         int ctas_per_sm = (dev->max_smem_optin + 1024) / (stage_smem + 1024);
         {
-            const int o = env_int("PUFF_ADV_CTAS_PER_SM", nst == 4 ? 2 : 0);
+            const int o = tune(PUFF_TUNE_CTAS_PER_SM, nst == 4 ? 2 : 0);
             if (o > 0 && o < ctas_per_sm) ctas_per_sm = o;
         }
         if (ctas_per_sm < 1) ctas_per_sm = 1;
@@ -1600,15 +1619,15 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             // per SM (more CTAs per SM lowered the achieved DRAM rate).  Buffers of only a few
             // chunks per SM (8192 x 64 and smaller) finish sooner on the single-warp kernel,
             // whose pipeline has fewer hops.
-            // PUFF_ADV_WS: 0 = single-warp, N = warp-specialised with N raw stages (2, 3, 4, 6).
+            // PUFF_TUNE_WS_STAGES: 0 = single-warp, N = warp-specialised with N raw stages (2, 3, 4, 6).
             const long long work_items = tiles * ((horizon + kChunkCols - 1) / kChunkCols);
-            const int ws = env_int("PUFF_ADV_WS", work_items >= 8LL * dev->sm_count ? 4 : 0);
+            const int ws = tune(PUFF_TUNE_WS_STAGES, work_items >= 8LL * dev->sm_count ? 4 : 0);
             if (ws != 0) {
                 const int wnst = ws <= 2 ? 2 : ws == 3 ? 3 : ws <= 5 ? 4 : 6;
                 const int smem = wnst * kStageBytes + 2 * kTermBytes + kWsOutSlots * kBoxBytes + 2048;
                 int per_sm = (dev->max_smem_optin + 1024) / (smem + 1024);
                 if (per_sm > 2) per_sm = 2;
-                { const int o = env_int("PUFF_ADV_CTAS_PER_SM", 0); if (o > 0) per_sm = o < 3 ? o : 3; }
+                { const int o = tune(PUFF_TUNE_CTAS_PER_SM, 0); if (o > 0) per_sm = o < 3 ? o : 3; }
                 if (per_sm < 1) per_sm = 1;
                 const long long mg = static_cast<long long>(dev->sm_count) * per_sm;
                 const int grid = static_cast<int>(tiles < mg ? tiles : mg);
@@ -1718,6 +1737,13 @@ extern "C" int puff_advantage_sm100_device_status(void)
         cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
     }
     return h;
+}
+
+extern "C" int puff_advantage_sm100_set_tuning(int knob, int value)
+{
+    if (knob < 0 || knob >= PUFF_TUNE_COUNT) return PUFF_ERR_VARIANT;
+    tune_init();
+    return g_tune[knob].exchange(value < 0 ? -1 : value, std::memory_order_relaxed);
 }
 
 extern "C" const char* puff_advantage_sm100_version(void) { return "0.1"; }

@@ -17,12 +17,11 @@ FORCE = {"tma2d": 1, "bulk1d": 2, "scan": 3, "generic": 4}
 
 
 @pytest.fixture(autouse=True)
-def _clear_force():
-    for k in ("PUFF_ADV_FORCE_KERNEL", "PUFF_ADV_STAGES", "PUFF_ADV_WS"):
-        os.environ.pop(k, None)
+def _clear_tuning():
+    from pufferlib_b200 import cabi
+    cabi.reset_tuning()
     yield
-    for k in ("PUFF_ADV_FORCE_KERNEL", "PUFF_ADV_STAGES", "PUFF_ADV_WS"):
-        os.environ.pop(k, None)
+    cabi.reset_tuning()
 
 
 def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=SENTINEL, stages=None, flags=0, ws=None):
@@ -32,20 +31,14 @@ def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=
     dev = [torch.as_tensor(np.asarray(t)).contiguous().cuda() for t in inputs]
     adv = torch.full_like(dev[0], sentinel)
     abs_sum = torch.full((dev[0].shape[0],), -1.0, device="cuda") if epilogue else None
-    if force is not None:
-        os.environ["PUFF_ADV_FORCE_KERNEL"] = str(FORCE[force])
-    if stages is not None:
-        os.environ["PUFF_ADV_STAGES"] = str(stages)
-    if ws is not None:
-        os.environ["PUFF_ADV_WS"] = str(ws)      # 0: single-warp tma2d, N: warp-specialised with N stages
+    # ws: 0 = single-warp tma2d, N = warp-specialised with N stages
+    cabi.set_tuning(force_kernel=None if force is None else FORCE[force], stages=stages, ws_stages=ws)
     try:
         launch_raw(*dev, adv, *hyper, seg_abs_sum=abs_sum, variant=variant, flags=flags)
         kernel = cabi.last_kernel()
         torch.cuda.synchronize()
     finally:
-        os.environ.pop("PUFF_ADV_FORCE_KERNEL", None)
-        os.environ.pop("PUFF_ADV_STAGES", None)
-        os.environ.pop("PUFF_ADV_WS", None)
+        cabi.reset_tuning()
     assert cabi.device_status() == 0
     return adv.cpu().numpy(), None if abs_sum is None else abs_sum.cpu().numpy(), kernel
 
@@ -185,7 +178,8 @@ def test_canaries_around_buffers(force, H):
     views[4].fill_(SENTINEL)
     before = [b.clone() for b in bufs[:4]]
     abs_buf = torch.full((S + 2 * pad,), 777.0, device="cuda")
-    os.environ["PUFF_ADV_FORCE_KERNEL"] = str(FORCE[force])
+    from pufferlib_b200 import cabi
+    cabi.set_tuning(force_kernel=FORCE[force])
     launch_raw(*views, *wl.hyper(), seg_abs_sum=abs_buf[pad:pad + S], variant="scan" if force == "scan" else "serial")
     torch.cuda.synchronize()
     for b, b0 in zip(bufs[:4], before):
