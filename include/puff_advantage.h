@@ -218,7 +218,8 @@ int puff_advantage_sm100_device_status(void);
 #define PUFF_TUNE_WS_STAGES     2   /* PUFF_ADV_WS: 0 = single-warp tma2d, N = warp-specialised with N stages */
 #define PUFF_TUNE_CTAS_PER_SM   3   /* PUFF_ADV_CTAS_PER_SM: cap on resident CTAs per SM of the tma2d kernels */
 #define PUFF_TUNE_LOAD_GROUP    4   /* PUFF_ADV_GROUP: chunks whose loads the warp-specialised producer issues together */
-#define PUFF_TUNE_COUNT         5
+#define PUFF_TUNE_SCAN_THREADS  5   /* PUFF_ADV_SCAN_THREADS: threads per row of the scan kernel (power of two, 32..1024) */
+#define PUFF_TUNE_COUNT         6
 int puff_advantage_sm100_set_tuning(int knob, int value);
 /* Library version, "major.minor". */
 const char* puff_advantage_sm100_version(void);

@@ -70,7 +70,7 @@ def load():
     return _lib
 
 
-TUNE = {"force_kernel": 0, "stages": 1, "ws_stages": 2, "ctas_per_sm": 3, "load_group": 4}
+TUNE = {"force_kernel": 0, "stages": 1, "ws_stages": 2, "ctas_per_sm": 3, "load_group": 4, "scan_threads": 5}
 
 
 def set_tuning(**knobs):
