@@ -98,8 +98,9 @@ extern "C" int puff_advantage_sm100_host(const float* h_values, const float* h_r
     HostPipe& p = g_pipe[device];
     std::lock_guard<std::mutex> lock(p.mu);
 
-    // row blocks of about PUFF_HOST_BLOCK_BYTES per array, a multiple of 32 rows
-    const long long target = env_ll("PUFF_HOST_BLOCK_BYTES", 8ll << 20);
+    // row blocks of about PUFF_HOST_BLOCK_BYTES (default 16 MB, measured best of 4..32 MB) per array,
+    // a multiple of 32 rows
+    const long long target = env_ll("PUFF_HOST_BLOCK_BYTES", 16ll << 20);
     long long block_rows = target / (horizon * 4);
     block_rows = (block_rows / 32) * 32;
     if (block_rows < 32) block_rows = 32;

@@ -387,3 +387,36 @@ def test_tma2d_forms_literal_paths(ws):
     assert np.isnan(want[:, 98]).all()
     got, _, _ = run_gpu([v, r, d, w], hyper, "serial", "tma2d", ws=ws)
     assert bits_equal(got, want), first_mismatch(got, want)
+
+
+@pytest.mark.parametrize("H,force", [(256, "tma2d"), (127, "bulk1d")])
+def test_more_than_2_31_elements(H, force):
+    """Element offsets beyond 2^31 (the reference's `int` offsets overflow there,
+    cuda/pufferlib.cu:48).  The buffer is a small block of rows repeated, so any
+    row block of the result must equal the oracle's result for that block."""
+    from pufferlib_b200.advantage import launch_raw
+    free, _ = torch.cuda.mem_get_info()
+    base_rows = 4096
+    reps = (2 ** 31) // (base_rows * H) + 3
+    S = base_rows * reps
+    need = 5 * S * H * 4 + (2 << 30)
+    if free < need:
+        pytest.skip(f"needs {need >> 30} GiB of free device memory")
+    wl = Workload("huge", base_rows, H, seed=123, done_p=0.02)
+    host = make_inputs(wl)
+    want = torch.from_numpy(oracle_advantage([t.numpy() for t in host], wl.hyper(), sentinel=SENTINEL)).cuda()
+    dev = [t.cuda().repeat(reps, 1) for t in host]
+    assert dev[0].numel() > 2 ** 31
+    adv = torch.full((S, H), SENTINEL, device="cuda")
+    abs_sum = torch.empty(S, device="cuda")
+    launch_raw(*dev, adv, *wl.hyper(), seg_abs_sum=abs_sum, variant="serial")
+    torch.cuda.synchronize()
+    from pufferlib_b200 import cabi
+    assert cabi.last_kernel() == force and cabi.device_status() == 0
+    for rep in (0, reps // 2, reps - 1):
+        got = adv[rep * base_rows:(rep + 1) * base_rows]
+        assert torch.equal(got.view(torch.int32), want.view(torch.int32)), rep
+    first = abs_sum[:base_rows]
+    assert torch.equal(abs_sum[(reps - 1) * base_rows:], first)
+    del dev, adv
+    torch.cuda.empty_cache()
