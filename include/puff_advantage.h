@@ -166,6 +166,21 @@ int puff_minibatch_sm100_gather(const float* advantages, const float* values,
 int puff_minibatch_sm100_bad_index(void);
 
 /*
+ * Rollout writer, on DEVICE buffers, asynchronous on `cuda_stream`: one
+ * environment step of rows [row_begin, row_begin + num_rows) into column
+ * `column` of the [num_segments, horizon] experience buffers.  Replaces
+ * pufferl.py:275 (clamp of the rewards to [-reward_clip, reward_clip];
+ * reward_clip <= 0 disables it) and :294-296 (rewards, terminals = done as
+ * 0/1 float, values).  step_dones is one byte per row (torch.bool).
+ */
+int puff_rollout_sm100_write(float* rewards, float* terminals, float* values,
+                             const float* step_rewards, const unsigned char* step_dones,
+                             const float* step_values, long long row_begin,
+                             long long num_rows, long long column,
+                             long long num_segments, long long horizon,
+                             float reward_clip, void* cuda_stream);
+
+/*
  * puff_priorities_sm100_weights for callers that cannot supply scratch.
  * (No counterpart in the reference, which allocates freely through torch.)
  *

@@ -16,4 +16,5 @@ from .advantage import (  # noqa: F401
     prioritized_sample_probs,
     priority_probs,
     priority_weights,
+    rollout_write,
 )

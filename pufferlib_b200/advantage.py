@@ -80,6 +80,15 @@ def minibatch_gather(advantages, values, prio_probs, idx, anneal_beta):
     return _ops().puff_minibatch_gather(advantages, values, prio_probs, idx, anneal_beta)
 
 
+def rollout_write(rewards, terminals, values, step_rewards, step_dones, step_values,
+                  row_begin, column, reward_clip=1.0):
+    """One environment step into column `column` of the experience buffers for
+    rows [row_begin, row_begin + len(step_rewards)): the clamp of pufferl.py:275
+    and the three column assignments of :294-296 in one launch."""
+    _ops().puff_rollout_write(rewards, terminals, values, step_rewards, step_dones, step_values.flatten(),
+                              row_begin, column, reward_clip)
+
+
 def prioritized_sample_probs(values, rewards, terminals, ratio, advantages,
                              gamma, gae_lambda, vtrace_rho_clip, vtrace_c_clip, prio_alpha,
                              process_group=None):

@@ -30,7 +30,7 @@ CABI_LIB = os.path.join(HERE, "libpuff_advantage_sm100.so")
 TORCH_EXT = os.path.join(HERE, "_C.so")
 
 CU_SOURCES = ["puff_advantage_sm100.cu", "puff_priorities_sm100.cu", "puff_minibatch_sm100.cu",
-              "puff_host_pipeline.cu"]
+              "puff_rollout_sm100.cu", "puff_host_pipeline.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -41,6 +41,7 @@ SIGNATURES = {
     "puff_minibatch_sm100_scratch_bytes": (ctypes.c_size_t, [_LL]),
     "puff_minibatch_sm100_gather": (_I, [_P] * 9 + [_F, _LL, _LL, _LL, _P, ctypes.c_size_t, _P]),
     "puff_minibatch_sm100_bad_index": (_I, []),
+    "puff_rollout_sm100_write": (_I, [_P] * 6 + [_LL] * 5 + [_F, _P]),
     "puff_priorities_sm100_weights_noalloc": (_I, [_P, _P, _P, _F, _LL, _P]),
     "puff_advantage_sm100_strerror": (ctypes.c_char_p, [_I]),
     "puff_advantage_sm100_last_kernel": (_I, []),

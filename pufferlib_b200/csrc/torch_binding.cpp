@@ -227,6 +227,38 @@ puff_minibatch_gather_cuda(torch::Tensor advantages, torch::Tensor values, torch
     return {mb_values, mb_returns, mb_raw, mb_norm, mb_prio};
 }
 
+// pufferl.py:275, 294-296 for a contiguous block of rows.
+void puff_rollout_write_cuda(torch::Tensor rewards, torch::Tensor terminals, torch::Tensor values,
+                             torch::Tensor step_rewards, torch::Tensor step_dones, torch::Tensor step_values,
+                             int64_t row_begin, int64_t column, double reward_clip)
+{
+    TORCH_CHECK(rewards.is_cuda(), "All tensors must be on GPU");
+    for (const torch::Tensor& t : {rewards, terminals, values}) {
+        TORCH_CHECK(t.dim() == 2 && t.sizes() == rewards.sizes(), "buffers must be 2D of one shape");
+        TORCH_CHECK(t.dtype() == torch::kFloat32 && t.is_contiguous(), "buffers must be contiguous float32");
+        TORCH_CHECK(t.device() == rewards.device(), "All tensors must be on same device");
+    }
+    const int64_t n = step_rewards.numel();
+    TORCH_CHECK(step_dones.numel() == n && step_values.numel() == n, "step tensors must have one entry per row");
+    TORCH_CHECK(step_rewards.dtype() == torch::kFloat32 && step_values.dtype() == torch::kFloat32,
+                "step rewards and values must be float32");
+    TORCH_CHECK(step_dones.dtype() == torch::kBool || step_dones.dtype() == torch::kUInt8, "step dones must be bool");
+    for (const torch::Tensor& t : {step_rewards, step_dones, step_values}) {
+        TORCH_CHECK(t.is_contiguous() && t.device() == rewards.device(), "step tensors must be contiguous on the same device");
+    }
+    int rc;
+    {
+        const c10::cuda::CUDAGuard guard(rewards.device());
+        rc = puff_rollout_sm100_write(rewards.data_ptr<float>(), terminals.data_ptr<float>(), values.data_ptr<float>(),
+                                      step_rewards.data_ptr<float>(),
+                                      static_cast<const unsigned char*>(step_dones.data_ptr()),
+                                      step_values.data_ptr<float>(), row_begin, n, column, rewards.size(0),
+                                      rewards.size(1), static_cast<float>(reward_clip),
+                                      at::cuda::getCurrentCUDAStream().stream());
+    }
+    check_rc(rc, "puff_rollout_write");
+}
+
 // Shape-only kernels so the ops can be traced (torch.compile / fake tensors).
 void compute_puff_advantage_meta(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor,
                                  double, double, double, double) {}
@@ -241,6 +273,7 @@ TORCH_LIBRARY(pufferlib, m)
     m.def("compute_puff_advantage_fill(Tensor values, Tensor rewards, Tensor dones, Tensor importance, Tensor(a!) advantages, Tensor(b!)? seg_abs_sum, float gamma, float lambda, float rho_clip, float c_clip) -> ()");
     m.def("puff_priority_weights(Tensor seg_abs_sum, float alpha) -> (Tensor, Tensor)");
     m.def("puff_priority_probs(Tensor weights, Tensor total_w) -> Tensor");
+    m.def("puff_rollout_write(Tensor(a!) rewards, Tensor(b!) terminals, Tensor(c!) values, Tensor step_rewards, Tensor step_dones, Tensor step_values, int row_begin, int column, float reward_clip) -> ()");
     m.def("puff_minibatch_gather(Tensor advantages, Tensor values, Tensor prio_probs, Tensor idx, float anneal_beta) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
 }
 
@@ -252,6 +285,7 @@ TORCH_LIBRARY_IMPL(pufferlib, CUDA, m)
     m.impl("puff_priority_weights", &puff_priority_weights_cuda);
     m.impl("puff_priority_probs", &puff_priority_probs_cuda);
     m.impl("puff_minibatch_gather", &puff_minibatch_gather_cuda);
+    m.impl("puff_rollout_write", &puff_rollout_write_cuda);
 }
 
 TORCH_LIBRARY_IMPL(pufferlib, Meta, m)

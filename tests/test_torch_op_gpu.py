@@ -237,3 +237,30 @@ def test_minibatch_gather_flags_bad_indices():
     assert cabi.load().puff_minibatch_sm100_bad_index() == 1
     assert cabi.load().puff_minibatch_sm100_bad_index() == 0      # cleared by the read
     assert torch.equal(mv[:2], val[idx[:2]]) and torch.all(mv[2:] == 0)
+
+
+def test_rollout_write_matches_the_trainer_assignments():
+    """pufferl.py:275, 294-296 in one launch; then the advantage op on the
+    buffers it filled equals the op on buffers filled the reference's way."""
+    import pufferlib_b200
+    S, H, lo, n = 300, 48, 37, 200
+    g = torch.Generator().manual_seed(11)
+    bufs = [torch.zeros(S, H, device="cuda") for _ in range(3)]
+    refs = [torch.zeros(S, H, device="cuda") for _ in range(3)]
+    for col in range(H):
+        r = (torch.randn(n, generator=g) * 2).cuda()
+        r[3] = float("nan")
+        d = (torch.rand(n, generator=g) < 0.1).cuda()
+        v = torch.randn(n, 1, generator=g).cuda()
+        pufferlib_b200.rollout_write(*bufs, r, d, v, lo, col)
+        rows = slice(lo, lo + n)
+        rc = torch.clamp(r, -1, 1)
+        refs[0][rows, col] = rc
+        refs[1][rows, col] = d.float()
+        refs[2][rows, col] = v.flatten()
+    for b, e in zip(bufs, refs):
+        assert torch.equal(torch.nan_to_num(b, 7.0), torch.nan_to_num(e, 7.0))
+    with pytest.raises(RuntimeError):
+        pufferlib_b200.rollout_write(*bufs, r, d, v, S - 10, 0)       # rows past the end
+    with pytest.raises(RuntimeError):
+        pufferlib_b200.rollout_write(*bufs, r, d, v, 0, H)            # column past the end
