@@ -117,17 +117,22 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+// One try_wait.  The suspend-time hint lets the hardware park the thread until the phase
+// completes (or the hint runs out) instead of spinning through the loop below: most warps
+// of the warp-specialised kernel spend most of their time waiting, and a spinning warp
+// costs issue slots and power that the memory-bound kernel pays for in clock speed.
+constexpr uint32_t kWaitHintNs = 200000u;
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
         : "memory");
     return ok;
 }
@@ -146,7 +151,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity)
         uint32_t polls = 0;
         while (!ok && polls < kWaitLimit) {
             ok = mbar_try_wait(bar, parity);
-            if ((++polls & 1023u) == 0u && global_ns() - t0 > kWaitLimitNs) break;
+            if (!ok && ((++polls & 15u) == 0u) && global_ns() - t0 > kWaitLimitNs) break;
         }
     }
     return __all_sync(0xffffffffu, ok != 0);
@@ -540,7 +545,7 @@ __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity)
         uint32_t polls = 0;
         while (!ok && polls < kWaitLimit) {
             ok = mbar_try_wait(bar, parity);
-            if ((++polls & 1023u) == 0u && global_ns() - t0 > kWaitLimitNs) break;
+            if (!ok && ((++polls & 15u) == 0u) && global_ns() - t0 > kWaitLimitNs) break;
         }
     }
     return ok != 0;
@@ -710,16 +715,50 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             first_r = r[0];
             first_d = d[0];
             const int col0 = c * kChunkCols + 8 * g;
-            float dl[8], kk[8], gc[8], nn[8];
+            float dl[8], kk[8];
             uint32_t nonbin = 0u;
+            if (col0 + 8 < horizon) {
+                // all eight columns have a step: the f32x2 forms of the same IEEE operations,
+                // two steps per instruction.  Steps (j, j+1) with odd j take their t+1
+                // operands (j+1, j+2) from aligned register pairs of the 128-bit loads.
+                const float2 neg1 = make_float2(-1.0f, -1.0f), one2 = make_float2(1.0f, 1.0f);
+                const float2 gamma2 = make_float2(gamma, gamma), gl2 = make_float2(gl, gl);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const bool valid = col0 + j < horizon - 1;
-                adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dl[j], gc[j], nn[j]);
-                dl[j] = valid ? dl[j] : 0.0f;
-                gc[j] = valid ? gc[j] : 0.0f;
-                kk[j] = __fmul_rn(gc[j], nn[j]);
-                nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nn[j])) : 0u;
+                for (int j = 1; j < 7; j += 2) {
+                    const float2 dn = make_float2(d[j + 1], d[j + 2]);
+                    const float2 nn2 = __ffma2_rn(dn, neg1, one2);   // 1 - d: exact product, one rounding
+                    const float2 t2 = __fadd2_rn(make_float2(r[j + 1], r[j + 2]),
+                                                 __fmul2_rn(__fmul2_rn(gamma2, make_float2(v[j + 1], v[j + 2])), nn2));
+                    const float2 td2 = make_float2(__fsub_rn(t2.x, v[j]), __fsub_rn(t2.y, v[j + 1]));
+                    const float2 rho2 = make_float2(fminf(w[j], rho_clip), fminf(w[j + 1], rho_clip));
+                    const float2 c2 = make_float2(fminf(w[j], c_clip), fminf(w[j + 1], c_clip));
+                    const float2 d2 = __fmul2_rn(rho2, td2);
+                    const float2 k2 = __fmul2_rn(__fmul2_rn(gl2, c2), nn2);
+                    const float2 q2 = __fmul2_rn(dn, nn2);
+                    nonbin |= __float_as_uint(q2.x) | __float_as_uint(q2.y);
+                    dl[j] = d2.x;
+                    dl[j + 1] = d2.y;
+                    kk[j] = k2.x;
+                    kk[j + 1] = k2.y;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j += 7) {   // steps 0 and 7
+                    float dj, gj, nj;
+                    adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
+                    dl[j] = dj;
+                    kk[j] = __fmul_rn(gj, nj);
+                    nonbin |= __float_as_uint(__fmul_rn(d[j + 1], nj));
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const bool valid = col0 + j < horizon - 1;
+                    float dj, gj, nj;
+                    adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
+                    dl[j] = valid ? dj : 0.0f;
+                    kk[j] = valid ? __fmul_rn(gj, nj) : 0.0f;
+                    nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nj)) : 0u;
+                }
             }
             const uint32_t tb = term_base + b * kTermBytes;
             sts128(tb + 0 * kBoxBytes + off0, make_float4(dl[0], dl[1], dl[2], dl[3]));
