@@ -518,10 +518,10 @@ def time_reference_cuda_kernel(sets, n_sets, hyper, elems):
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant
 # kernel from the ncu capture summarised in
-# profiles/tma2d_ws_kernel_cfg2_32768x256_ncu_full.md: 138.44 MB read + 16.32 MB written
+# profiles/tma2d_ws_kernel_cfg2_32768x256_ncu_full.md: 138.45 MB read + 15.64 MB written
 # on a 32768-segment case, scaled by the rows of a full launch (every row is read once,
 # so traffic grows in proportion).
-TRAFFIC = {("cfg2", "tma2d"): int((138.44e6 + 16.32e6) * 4)}
+TRAFFIC = {("cfg2", "tma2d"): int((138.45e6 + 15.64e6) * 4)}
 
 
 def main():
