@@ -516,6 +516,76 @@ def time_reference_cuda_kernel(sets, n_sets, hyper, elems):
         return {"error": str(exc)[:200]}
 
 
+def run_sequence_arm(args, wl):
+    """--sequence: the trainer's per-minibatch sequence around the op
+    (pufferl.py:346-375, 408-409) as the reference writes it -- eager torch
+    kernels around the 9-argument op -- against the same sequence on the fused
+    entry points, both eager on one GPU, same buffers, same sampled indices."""
+    import pufferlib_b200
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    S, H = wl.segments, wl.horizon
+    hyper = wl.hyper()
+    values, rewards, terminals, ratio = [t.to(dev) for t in make_inputs(wl)]
+    M = max(1, S // 16)                      # nmmo3.ini: 32768 / 64 = 512 of 8192 segments
+    a, beta = PRIO_ALPHA, 0.6
+    gen = torch.Generator(device=dev)
+
+    def reference_style():
+        advantages = torch.zeros((S, H), device=dev)
+        pufferlib_b200.compute_puff_advantage(values, rewards, terminals, ratio, advantages, *hyper)
+        adv = advantages.abs().sum(axis=1)
+        prio_weights = torch.nan_to_num(adv ** a, 0, 0, 0)
+        prio_probs = (prio_weights + 1e-6) / (prio_weights.sum() + 1e-6)
+        idx = torch.multinomial(prio_probs, M, generator=gen)
+        mb_prio = (S * prio_probs[idx, None]) ** -beta
+        mb_values = values[idx]
+        mb_returns = advantages[idx] + mb_values
+        mb_advantages = advantages[idx]
+        adv_n = mb_prio * (mb_advantages - mb_advantages.mean()) / (mb_advantages.std() + 1e-8)
+        return idx, mb_values, mb_returns, adv_n
+
+    sums = torch.empty(S, device=dev)
+    advantages = torch.empty((S, H), device=dev)
+
+    def fused():
+        pufferlib_b200.compute_puff_advantage_fill(values, rewards, terminals, ratio, *hyper,
+                                                   advantages=advantages, seg_abs_sum=sums)
+        weights, total = pufferlib_b200.priority_weights(sums, a)
+        prio_probs = pufferlib_b200.priority_probs(weights, total)
+        idx = torch.multinomial(prio_probs, M, generator=gen)
+        mb_values, mb_returns, _, adv_n, _ = pufferlib_b200.minibatch_gather(advantages, values, prio_probs, idx, beta)
+        return idx, mb_values, mb_returns, adv_n
+
+    # same sampled indices -> same results
+    gen.manual_seed(1)
+    r1 = reference_style()
+    gen.manual_seed(1)
+    r2 = fused()
+    same_idx = bool(torch.equal(r1[0], r2[0]))
+    max_err = float((r1[3] - r2[3]).abs().max()) if same_idx else None
+
+    def timeit(fn, n):
+        for _ in range(10):
+            fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / n
+
+    n = max(20, args.steps if args.steps < 2000 else 500)
+    t_ref = timeit(reference_style, n)
+    t_fused = timeit(fused, n)
+    print(json.dumps({
+        "mode": "sequence", "workload": f"{wl.name}: {S}x{H}, minibatch {M} segments",
+        "reference_style_us": 1e6 * t_ref, "fused_us": 1e6 * t_fused, "ratio": t_ref / t_fused,
+        "same_sampled_indices": same_idx, "max_abs_diff_normalised_advantages": max_err,
+        "what": "eager launches, wall clock per minibatch sequence (pufferl.py:352-375, 408-409); "
+                "reference_style = torch.zeros + this repo's 9-argument op + the reference's eager torch lines"}), flush=True)
+
+
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant
 # kernel from the ncu capture summarised in
 # profiles/tma2d_ws_kernel_cfg2_32768x256_ncu_full.md: 138.45 MB read + 15.64 MB written
@@ -534,6 +604,8 @@ def main():
     ap.add_argument("--variant", default="auto", choices=["auto", "serial", "scan", "generic"])
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sequence", action="store_true",
+                    help="time the trainer's per-minibatch sequence (eager reference lines vs fused entry points)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="run the priority launches and the all-reduce on the kernel's stream")
     ap.add_argument("--no-graph", action="store_true", help="never capture the timed loop into CUDA graphs")
@@ -552,6 +624,9 @@ def main():
         wl = wl.with_segments(args.segments)
     if args.impl == "reference":
         run_reference_arm(args, wl, rank, world)
+        return
+    if args.sequence:
+        run_sequence_arm(args, wl)
         return
     if args.gpus > 1 and world == 1:
         raise SystemExit("launch with torchrun: python -m torch.distributed.run --nnodes=1 "
