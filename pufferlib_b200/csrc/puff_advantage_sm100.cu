@@ -898,16 +898,18 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
 // One CTA of four warps per tile, one stage of shared memory (v | r | d | w,
 // dense, pitch H); several CTAs per SM overlap each other's phases:
 //   1. thread 0 issues four cp.async.bulk copies, everybody waits on the mbarrier
-//   2. terms, all 128 threads over the flat tile: delta, k = gc*nn, gc, nn of
-//      every step, written in place (delta -> w, k -> r, gc -> d, nn -> v).  Element
-//      e is read only by the threads that own e and e-1, so a batch that reads
-//      all its operands, synchronises, then writes cannot clobber live inputs.
-//   3. chain, warp 0: lane r walks row r, A = delta + k*A, A written over k
-//      (stride H words: conflict-free for odd H); literal order from gc and nn
-//      when a non-binary nn was seen or A nears the overflow range
+//   2. terms, all 128 threads over the flat tile in units of four elements:
+//      delta and k = (gamma*lambda*c)*nn of every step go to registers; after one
+//      barrier (every raw operand has been read) they are written as interleaved
+//      (delta, k) pairs over the d | w region
+//   3. chain, warp 0: lane r walks row r with one 64-bit shared load per step,
+//      A = delta + k*A, A written into the v region (stride H words: conflict-free
+//      for odd H).  A non-binary nn or advantages near the overflow range send the
+//      tile down the reference's literal order, operands straight from global memory
 //   4. copy-out, all threads: coalesced 128-bit stores that skip column H-1
 constexpr int kB1Threads = 128;
-constexpr int kB1Batch = 4;   // elements per thread between synchronisations
+constexpr int kB1MaxUnits = 9;                                   // units of four elements per thread
+constexpr int kB1MaxElems = kB1Threads * kB1MaxUnits * 4;         // elements per tile (72 KB of stage)
 
 __global__ void __launch_bounds__(kB1Threads)
 puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
@@ -947,40 +949,45 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
         const uint32_t bytes = static_cast<uint32_t>(n_el) * 4u;
         const long long goff = tile * tile_elems;
         // ---- 1. fetch ----
-        if ((bytes & 15u) == 0u) {
-            if (tid == 0) {
-                mbar_expect_tx(bar, 4u * bytes);
-                for (int a = 0; a < 4; ++a) bulk_load_1d(base + a * arr_pitch, src[a] + goff, bytes, bar);
+        // bulk copies for the 16-byte multiple of the span (all of it, except in a last tile
+        // whose row count makes the byte size ragged), plain loads for the up to three
+        // trailing floats of each array
+        {
+            const uint32_t bulk_bytes = bytes & ~15u;
+            if (bulk_bytes != 0u) {
+                if (tid == 0) {
+                    mbar_expect_tx(bar, 4u * bulk_bytes);
+                    for (int a = 0; a < 4; ++a) bulk_load_1d(base + a * arr_pitch, src[a] + goff, bulk_bytes, bar);
+                }
             }
-            if (!mbar_wait_thread(bar, parity)) failed = true;
-            parity ^= 1u;
+            const int first_tail = static_cast<int>(bulk_bytes >> 2);
+            if (tid < 4 * (n_el - first_tail)) {   // at most 12 threads
+                const int a = tid / (n_el - first_tail), e = first_tail + tid % (n_el - first_tail);
+                (smem_f + (a * arr_pitch) / 4)[e] = __ldg(src[a] + goff + e);
+            }
+            if (bulk_bytes != 0u) {
+                if (!mbar_wait_thread(bar, parity)) failed = true;
+                parity ^= 1u;
+            }
             if (__syncthreads_or(failed)) {
                 failed = true;
                 break;
             }
-        } else {
-            for (int a = 0; a < 4; ++a) {
-                const float* g = src[a] + goff;
-                float* d = smem_f + (a * arr_pitch) / 4;
-                for (int e = tid; e < n_el; e += kB1Threads) d[e] = __ldg(g + e);
-            }
-            __syncthreads();
         }
-        // ---- 2. terms, in place ----
-        // a thread owns groups of four consecutive elements (one 16-byte unit per
-        // array); the operand at e+4 comes from the next unit
+        // ---- 2. terms ----
+        // a thread owns units of four consecutive elements (one 16-byte unit per array);
+        // the operand at e+4 comes from the next unit
         uint32_t nonbin = 0u;
         const int n_grp = (n_el + 3) >> 2;
         const int grp_stride_cols = (4 * kB1Threads) % horizon;
-        int col_g = (4 * tid) % horizon;   // column of the first element of this thread's next group
-        for (int g0 = 0; g0 < n_grp; g0 += kB1Threads * kB1Batch) {
-            float4 dl4[kB1Batch], kk4[kB1Batch], gc4[kB1Batch], nn4[kB1Batch];
+        float4 dl4[kB1MaxUnits], kk4[kB1MaxUnits];
+        {
+            int col_g = (4 * tid) % horizon;   // column of the first element of this thread's next unit
 #pragma unroll
-            for (int u = 0; u < kB1Batch; ++u) {
-                const int grp = g0 + u * kB1Threads + tid;
+            for (int u = 0; u < kB1MaxUnits; ++u) {
+                const int grp = u * kB1Threads + tid;
                 const int e = grp << 2;
                 float dl[4] = {0.0f, 0.0f, 0.0f, 0.0f}, kk[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                float gc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, nn[4] = {1.0f, 1.0f, 1.0f, 1.0f};
                 if (grp < n_grp) {
                     // the arrays are padded to 16 bytes, so a unit that straddles n_el is readable
                     const float4 v4 = *reinterpret_cast<const float4*>(sv + e);
@@ -1002,31 +1009,26 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                         float dj, gj, nj;
                         adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
                         dl[j] = valid ? dj : 0.0f;
-                        gc[j] = valid ? gj : 0.0f;
-                        nn[j] = valid ? nj : 1.0f;
-                        kk[j] = __fmul_rn(gc[j], nn[j]);
+                        kk[j] = valid ? __fmul_rn(gj, nj) : 0.0f;
                         nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nj)) : 0u;
                         col = col + 1 == horizon ? 0 : col + 1;
                     }
                 }
                 dl4[u] = make_float4(dl[0], dl[1], dl[2], dl[3]);
                 kk4[u] = make_float4(kk[0], kk[1], kk[2], kk[3]);
-                gc4[u] = make_float4(gc[0], gc[1], gc[2], gc[3]);
-                nn4[u] = make_float4(nn[0], nn[1], nn[2], nn[3]);
                 col_g += grp_stride_cols;
                 if (col_g >= horizon) col_g -= horizon;
             }
-            __syncthreads();   // every operand of this batch has been read
+        }
+        __syncthreads();   // every raw operand of the tile has been read
+        float2* const st = reinterpret_cast<float2*>(sd);   // (delta, k) pairs over the d | w region
 #pragma unroll
-            for (int u = 0; u < kB1Batch; ++u) {
-                const int grp = g0 + u * kB1Threads + tid;
-                const int e = grp << 2;
-                if (grp < n_grp) {
-                    *reinterpret_cast<float4*>(swt + e) = dl4[u];
-                    *reinterpret_cast<float4*>(sr + e) = kk4[u];
-                    *reinterpret_cast<float4*>(sd + e) = gc4[u];
-                    *reinterpret_cast<float4*>(sv + e) = nn4[u];
-                }
+        for (int u = 0; u < kB1MaxUnits; ++u) {
+            const int grp = u * kB1Threads + tid;
+            const int e = grp << 2;
+            if (grp < n_grp) {
+                *reinterpret_cast<float4*>(st + e) = make_float4(dl4[u].x, kk4[u].x, dl4[u].y, kk4[u].y);
+                *reinterpret_cast<float4*>(st + e + 2) = make_float4(dl4[u].z, kk4[u].z, dl4[u].w, kk4[u].w);
             }
         }
         const bool any_nonbin = __syncthreads_or((nonbin << 1) != 0u);
@@ -1035,42 +1037,42 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
             const int lane = tid;
             const int ro = lane * horizon;
             const bool mine = lane < rows;
-            float a_run = 0.0f, abs_run = 0.0f, big = 0.0f;
+            float a_run = 0.0f, abs_run = 0.0f;
             bool literal = any_nonbin;
             if (!literal) {
                 if (mine) {
                     int t = horizon - 2;
                     for (; t >= 7; t -= 8) {   // eight steps' operands first, then the dependent part
-                        float d8[8], k8[8];
+                        float2 p8[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) p8[j] = st[ro + t - j];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            d8[j] = swt[ro + t - j];
-                            k8[j] = sr[ro + t - j];
-                        }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            a_run = __fadd_rn(d8[j], __fmul_rn(k8[j], a_run));
-                            sr[ro + t - j] = a_run;
+                            a_run = __fadd_rn(p8[j].x, __fmul_rn(p8[j].y, a_run));
+                            sv[ro + t - j] = a_run;
                             abs_run = __fadd_rn(abs_run, fabsf(a_run));
-                            big = fmaxf(big, fabsf(a_run));
                         }
                     }
                     for (; t >= 0; --t) {
-                        a_run = __fadd_rn(swt[ro + t], __fmul_rn(sr[ro + t], a_run));
-                        sr[ro + t] = a_run;
+                        const float2 pr = st[ro + t];
+                        a_run = __fadd_rn(pr.x, __fmul_rn(pr.y, a_run));
+                        sv[ro + t] = a_run;
                         abs_run = __fadd_rn(abs_run, fabsf(a_run));
-                        big = fmaxf(big, fabsf(a_run));
                     }
                 }
-                literal = __any_sync(0xffffffffu, !(big <= 1e30f));
+                // the running sum of |A| bounds every |A| of the row
+                literal = __any_sync(0xffffffffu, !(abs_run <= 1e30f));
             }
-            if (literal) {   // rare: the reference's literal order
+            if (literal) {   // rare: the reference's literal order, operands straight from global memory
                 a_run = 0.0f;
                 abs_run = 0.0f;
                 if (mine) {
+                    const long long gro = goff + ro;
                     for (int t = horizon - 2; t >= 0; --t) {
-                        a_run = __fadd_rn(swt[ro + t], __fmul_rn(__fmul_rn(sd[ro + t], a_run), sv[ro + t]));
-                        sr[ro + t] = a_run;
+                        a_run = adv_step(__ldg(values + gro + t), __ldg(importance + gro + t), __ldg(values + gro + t + 1),
+                                         __ldg(rewards + gro + t + 1), __ldg(dones + gro + t + 1), a_run, gamma, gl,
+                                         rho_clip, c_clip);
+                        sv[ro + t] = a_run;
                         abs_run = __fadd_rn(abs_run, fabsf(a_run));
                     }
                 }
@@ -1078,14 +1080,14 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
             if (mine && seg_abs_sum != nullptr) seg_abs_sum[tile * tile_rows + lane] = abs_run;
         }
         __syncthreads();
-        // ---- 4. copy-out (advantages are in the r slot), column H-1 of every row skipped ----
+        // ---- 4. copy-out (advantages are in the v region), column H-1 of every row skipped ----
         {
             float* const g = advantages + goff;
             const int n4 = n_el >> 2;   // the tile starts on a 16-byte boundary
             int col = (4 * tid) % horizon;
             for (int e4 = tid; e4 < n4; e4 += kB1Threads) {
                 const int e = e4 << 2;
-                const float4 a4 = *reinterpret_cast<const float4*>(sr + e);
+                const float4 a4 = *reinterpret_cast<const float4*>(sv + e);
                 if (col + 4 < horizon) {
                     *reinterpret_cast<float4*>(g + e) = a4;
                 } else {
@@ -1102,7 +1104,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                 if (col >= horizon) col -= horizon;
             }
             for (int e = (n4 << 2) + tid; e < n_el; e += kB1Threads) {
-                if (e % horizon != horizon - 1) g[e] = sr[e];
+                if (e % horizon != horizon - 1) g[e] = sv[e];
                 else if (zero_last) g[e] = 0.0f;
             }
         }
@@ -1505,30 +1507,22 @@ static bool ranges_overlap(const void* a, size_t na, const void* b, size_t nb)
     return a0 < b0 + nb && b0 < a0 + na;
 }
 
-// bulk1d tile height: 32 rows when one stage stays within ~72 KB (three CTAs
-// per SM), otherwise the largest of 16/8/4 rows that does, otherwise the largest
-// that fits at all; 0 when even four rows do not fit
+// bulk1d tile height: the largest of 32/16/8/4 rows whose tile holds at most kB1MaxElems
+// elements (72 KB of stage: three CTAs per SM, and every thread can keep the terms of its
+// units in registers); 0 when even four rows do not fit
 static int bulk1d_tile_rows(long long horizon, int max_smem, size_t* smem_bytes)
 {
     const int cand[4] = {32, 16, 8, 4};
-    int best = 0;
-    size_t best_bytes = 0;
     for (int i = 0; i < 4; ++i) {
+        if (static_cast<long long>(cand[i]) * horizon > kB1MaxElems) continue;
         const size_t arr = (static_cast<size_t>(cand[i]) * horizon * 4 + 15) & ~static_cast<size_t>(15);
         const size_t need = 4 * arr + 16 + 128;
         if (need > static_cast<size_t>(max_smem)) continue;
-        if (best == 0) {
-            best = cand[i];
-            best_bytes = need;
-        }
-        if (need <= 72 * 1024) {
-            best = cand[i];
-            best_bytes = need;
-            break;
-        }
+        *smem_bytes = need;
+        return cand[i];
     }
-    *smem_bytes = best_bytes;
-    return best;
+    *smem_bytes = 0;
+    return 0;
 }
 
 }  // namespace puff
