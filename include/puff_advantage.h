@@ -229,7 +229,7 @@ int puff_advantage_sm100_device_status(void);
  * unknown knob).  The initial values come from the environment variables named
  * beside each knob, read once. */
 #define PUFF_TUNE_FORCE_KERNEL  0   /* PUFF_ADV_FORCE_KERNEL: a PUFF_KERNEL_* to use whenever it applies */
-#define PUFF_TUNE_STAGES        1   /* PUFF_ADV_STAGES: ring depth of the single-warp tma2d kernel (2,3,4,6,8,12) */
+#define PUFF_TUNE_STAGES        1   /* PUFF_ADV_STAGES: ring depth of the single-warp tma2d kernel (2, 3, 4) */
 #define PUFF_TUNE_WS_STAGES     2   /* PUFF_ADV_WS: 0 = single-warp tma2d, N = warp-specialised with N stages */
 #define PUFF_TUNE_CTAS_PER_SM   3   /* PUFF_ADV_CTAS_PER_SM: cap on resident CTAs per SM of the tma2d kernels */
 #define PUFF_TUNE_LOAD_GROUP    4   /* PUFF_ADV_GROUP: chunks whose loads the warp-specialised producer issues together */

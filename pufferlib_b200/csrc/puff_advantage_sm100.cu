@@ -188,10 +188,6 @@ __device__ __forceinline__ void bulk_wait_read()
 {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
-__device__ __forceinline__ void bulk_wait_all()
-{
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
@@ -501,7 +497,9 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
         }
     }
     if (lane == 0) {
-        bulk_wait_all();
+        // the stores only have to be done reading shared memory before the CTA exits;
+        // their global writes complete with the grid
+        bulk_wait_read<0>();
         if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
     }
 }
@@ -880,7 +878,9 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             if (++oslot == kWsOutSlots) oslot = 0;
         }
         if (lane == 0) {
-            bulk_wait_all();
+            // the stores only have to be done reading shared memory before the CTA exits;
+            // their global writes complete with the grid
+            bulk_wait_read<0>();
             if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
         }
     }
@@ -1378,9 +1378,6 @@ static const DeviceInfo* device_info(int* code)
                 set_tma2d_attrs<2>();
                 set_tma2d_attrs<3>();
                 set_tma2d_attrs<4>();
-                set_tma2d_attrs<6>();
-                set_tma2d_attrs<8>();
-                set_tma2d_attrs<12>();
                 set_tma2d_ws_attrs<2, 2>();
                 set_tma2d_ws_attrs<3, 2>();
                 set_tma2d_ws_attrs<4, 2>();
@@ -1624,7 +1621,7 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
         // measured on cfg2 (131072 x 256): two CTAs per SM with a four-stage ring each
         // beat both more, shallower CTAs and one deeper CTA
         int nst = tune(PUFF_TUNE_STAGES, 4);
-        nst = nst <= 2 ? 2 : nst == 3 ? 3 : nst == 4 ? 4 : nst <= 6 ? 6 : nst <= 8 ? 8 : 12;
+        nst = nst <= 2 ? 2 : nst == 3 ? 3 : 4;
         const int stage_smem = nst * kStageBytes + 2 * kBoxBytes + nst * 8 + 1024;
         int ctas_per_sm = (dev->max_smem_optin + 1024) / (stage_smem + 1024);
         {
@@ -1682,10 +1679,7 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             switch (nst) {
                 case 2: PUFF_TMA2D_CASE(2); break;
                 case 3: PUFF_TMA2D_CASE(3); break;
-                case 4: PUFF_TMA2D_CASE(4); break;
-                case 6: PUFF_TMA2D_CASE(6); break;
-                case 8: PUFF_TMA2D_CASE(8); break;
-                default: PUFF_TMA2D_CASE(12); break;
+                default: PUFF_TMA2D_CASE(4); break;
             }
 #undef PUFF_TMA2D_CASE
             g_launch_count.fetch_add(1, std::memory_order_relaxed);
