@@ -116,8 +116,20 @@ extern "C" int puff_advantage_sm100_host(const float* h_values, const float* h_r
     } else {
         int slot = 0;
         const float* h_in[4] = {h_values, h_rewards, h_dones, h_importance};
-        for (long long r0 = 0; r0 < num_segments && rc == PUFF_OK; r0 += block_rows, slot = (slot + 1) % kSlots) {
-            const long long rows = num_segments - r0 < block_rows ? num_segments - r0 : block_rows;
+        // full blocks through the body; the last two blocks' worth of rows is cut into halves
+        // of what remains, so that the kernel and the download that trail the last upload
+        // are short (the uploads are what the wall time is made of)
+        const long long min_rows = env_ll("PUFF_HOST_TAPER", 1) != 0 ? ((1ll << 20) / (horizon * 4) / 32 + 1) * 32 : block_rows;
+        long long rows = 0;
+        for (long long r0 = 0; r0 < num_segments && rc == PUFF_OK; r0 += rows, slot = (slot + 1) % kSlots) {
+            const long long left = num_segments - r0;
+            rows = block_rows;
+            if (left <= 2 * block_rows && min_rows < block_rows) {
+                rows = ((left / 2 + 31) / 32) * 32;
+                if (rows < min_rows) rows = min_rows;
+                if (rows > block_rows) rows = block_rows;
+            }
+            if (rows > left) rows = left;
             const size_t n = static_cast<size_t>(rows) * horizon;
             const size_t off = static_cast<size_t>(r0) * horizon;
             cudaStream_t st = p.stream[slot];
