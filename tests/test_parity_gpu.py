@@ -420,3 +420,34 @@ def test_more_than_2_31_elements(H, force):
     assert torch.equal(abs_sum[(reps - 1) * base_rows:], first)
     del dev, adv
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("ws", [0, 1])
+def test_bulk1d_forms(ws, golden_small):
+    """One-stage (0) and warp-specialised (1) forms of the odd-horizon kernel: golden
+    cases, ragged shapes, many tiles per CTA, literal path, fused sums, last column."""
+    from pufferlib_b200 import cabi
+    for name, case in golden_small.items():
+        if case["values"].shape[1] < 2:
+            continue
+        got, _, kernel = run_gpu([case[k] for k in KEYS], case["hyper"], "serial", "bulk1d", ws=ws)
+        assert kernel == "bulk1d"
+        assert bits_equal(got, case["advantages"]), f"{name}/ws={ws}: {first_mismatch(got, case['advantages'])}"
+    seed = 900
+    for S, H in ((1, 2), (3, 3), (33, 5), (70, 91), (1000, 127), (9000, 33), (5000, 91), (257, 301), (40, 1101), (64, 64)):
+        wl = Workload("b1", S, H, seed=seed, done_p=0.1)
+        seed += 1
+        inputs = [t.numpy() for t in make_inputs(wl)]
+        got, abs_sum, _ = run_gpu(inputs, wl.hyper(), "serial", "bulk1d", epilogue=True, ws=ws)
+        want = oracle_advantage(inputs, wl.hyper())
+        assert bits_equal(got, want), f"S={S} H={H} ws={ws}: {first_mismatch(got, want)}"
+        exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
+        np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6)
+        got0, _, _ = run_gpu(inputs, wl.hyper(), "serial", "bulk1d", ws=ws, flags=cabi.FLAG_ZERO_LAST_COLUMN)
+        assert bits_equal(got0, oracle_advantage(inputs, wl.hyper(), sentinel=0.0)), (S, H, ws)
+    wl = Workload("b1frac", 500, 91, seed=77)
+    v, r, d, w = [t.numpy() for t in make_inputs(wl)]
+    d = np.random.default_rng(2).random(d.shape).astype(np.float32)
+    want = oracle_advantage([v, r, d, w], wl.hyper())
+    got, _, _ = run_gpu([v, r, d, w], wl.hyper(), "serial", "bulk1d", ws=ws)
+    assert bits_equal(got, want), first_mismatch(got, want)
