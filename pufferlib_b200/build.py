@@ -68,7 +68,8 @@ def _run(cmd, verbose):
 
 def build_cabi(force=False, verbose=False, ptxas_info=False):
     sources = [os.path.join(CSRC, s) for s in CU_SOURCES]
-    deps = sources + [os.path.join(INCLUDE, "puff_advantage.h")]
+    headers = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cuh")]
+    deps = sources + headers + [os.path.join(INCLUDE, "puff_advantage.h")]
     if force or _stale(CABI_LIB, deps):
         flags = list(NVCC_FLAGS)
         if ptxas_info:

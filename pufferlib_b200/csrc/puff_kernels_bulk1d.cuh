@@ -1,0 +1,503 @@
+// Serial advantage kernels for H % 4 != 0 on dense row tiles fetched by 1-D bulk copies: one-stage and warp-specialised forms.
+// Included by puff_advantage_sm100.cu after puff_device.cuh.
+#pragma once
+#include "puff_device.cuh"
+
+namespace puff {
+
+// ---------------------------------------------------------------------------
+// bulk1d: serial, dense tiles of `tile_rows` whole rows fetched by 1-D bulk copies
+// ---------------------------------------------------------------------------
+// For H % 4 != 0 the row pitch is not a multiple of 16 bytes and no 2-D tensor
+// map exists, but a tile of whole rows is one contiguous span per array;
+// tile_rows is a multiple of 4, so every tile starts on a 16-byte boundary for
+// any H.  (The last tile of a buffer may have a byte size that is not a
+// multiple of 16: it is fetched with plain loads.)
+//
+// One CTA of four warps per tile, one stage of shared memory (v | r | d | w,
+// dense, pitch H); several CTAs per SM overlap each other's phases:
+//   1. thread 0 issues four cp.async.bulk copies, everybody waits on the mbarrier
+//   2. terms, all 128 threads over the flat tile in units of four elements:
+//      delta and k = (gamma*lambda*c)*nn of every step go to registers; after one
+//      barrier (every raw operand has been read) they are written as interleaved
+//      (delta, k) pairs over the d | w region
+//   3. chain, warp 0: lane r walks row r with one 64-bit shared load per step,
+//      A = delta + k*A, A written into the v region (stride H words: conflict-free
+//      for odd H).  A non-binary nn or advantages near the overflow range send the
+//      tile down the reference's literal order, operands straight from global memory
+//   4. copy-out, all threads: coalesced 128-bit stores that skip column H-1
+constexpr int kB1Threads = 128;
+constexpr int kB1MaxUnits = 9;                                   // units of four elements per thread
+constexpr int kB1MaxElems = kB1Threads * kB1MaxUnits * 4;         // elements per tile (72 KB of stage)
+
+__global__ void __launch_bounds__(kB1Threads)
+puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
+                       const float* __restrict__ dones, const float* __restrict__ importance,
+                       float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
+                       float lambda, float rho_clip, float c_clip, long long num_segments,
+                       int horizon, int tile_rows, long long num_tiles, int zero_last)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+    float* const smem_f = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
+    const int tid = threadIdx.x;
+    const int tile_elems = tile_rows * horizon;
+    const uint32_t arr_pitch = (static_cast<uint32_t>(tile_elems) * 4u + 15u) & ~15u;   // bytes, 16-byte aligned
+    const uint32_t bar = base + 4u * arr_pitch;
+    float* const sv = smem_f;
+    float* const sr = sv + arr_pitch / 4;
+    float* const sd = sr + arr_pitch / 4;
+    float* const swt = sd + arr_pitch / 4;
+
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    const float gl = __fmul_rn(gamma, lambda);
+    const float* const src[4] = {values, rewards, dones, importance};
+    uint32_t parity = 0u;
+    bool failed = false;
+
+    for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const long long rem = num_segments - tile * tile_rows;
+        const int rows = static_cast<int>(rem < tile_rows ? rem : tile_rows);
+        const int n_el = rows * horizon;
+        const uint32_t bytes = static_cast<uint32_t>(n_el) * 4u;
+        const long long goff = tile * tile_elems;
+        // ---- 1. fetch ----
+        // bulk copies for the 16-byte multiple of the span (all of it, except in a last tile
+        // whose row count makes the byte size ragged), plain loads for the up to three
+        // trailing floats of each array
+        {
+            const uint32_t bulk_bytes = bytes & ~15u;
+            if (bulk_bytes != 0u) {
+                if (tid == 0) {
+                    mbar_expect_tx(bar, 4u * bulk_bytes);
+                    for (int a = 0; a < 4; ++a) bulk_load_1d(base + a * arr_pitch, src[a] + goff, bulk_bytes, bar);
+                }
+            }
+            const int first_tail = static_cast<int>(bulk_bytes >> 2);
+            if (tid < 4 * (n_el - first_tail)) {   // at most 12 threads
+                const int a = tid / (n_el - first_tail), e = first_tail + tid % (n_el - first_tail);
+                (smem_f + (a * arr_pitch) / 4)[e] = __ldg(src[a] + goff + e);
+            }
+            if (bulk_bytes != 0u) {
+                if (!mbar_wait_thread(bar, parity)) failed = true;
+                parity ^= 1u;
+            }
+            if (__syncthreads_or(failed)) {
+                failed = true;
+                break;
+            }
+        }
+        // ---- 2. terms ----
+        // a thread owns units of four consecutive elements (one 16-byte unit per array);
+        // the operand at e+4 comes from the next unit
+        uint32_t nonbin = 0u;
+        const int n_grp = (n_el + 3) >> 2;
+        const int grp_stride_cols = (4 * kB1Threads) % horizon;
+        float4 dl4[kB1MaxUnits], kk4[kB1MaxUnits];
+        {
+            int col_g = (4 * tid) % horizon;   // column of the first element of this thread's next unit
+#pragma unroll
+            for (int u = 0; u < kB1MaxUnits; ++u) {
+                const int grp = u * kB1Threads + tid;
+                const int e = grp << 2;
+                float dl[4] = {0.0f, 0.0f, 0.0f, 0.0f}, kk[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (grp < n_grp) {
+                    // the arrays are padded to 16 bytes, so a unit that straddles n_el is readable
+                    const float4 v4 = *reinterpret_cast<const float4*>(sv + e);
+                    const float4 r4 = *reinterpret_cast<const float4*>(sr + e);
+                    const float4 d4 = *reinterpret_cast<const float4*>(sd + e);
+                    const float4 w4 = *reinterpret_cast<const float4*>(swt + e);
+                    const bool more = e + 4 < n_el;
+                    const float vn = more ? sv[e + 4] : 0.0f;
+                    const float rn = more ? sr[e + 4] : 0.0f;
+                    const float dn = more ? sd[e + 4] : 0.0f;
+                    const float v[5] = {v4.x, v4.y, v4.z, v4.w, vn};
+                    const float r[5] = {r4.x, r4.y, r4.z, r4.w, rn};
+                    const float d[5] = {d4.x, d4.y, d4.z, d4.w, dn};
+                    const float w[4] = {w4.x, w4.y, w4.z, w4.w};
+                    int col = col_g;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const bool valid = (col < horizon - 1) && (e + j < n_el);   // then e+j+1 is in the same row
+                        float dj, gj, nj;
+                        adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
+                        dl[j] = valid ? dj : 0.0f;
+                        kk[j] = valid ? __fmul_rn(gj, nj) : 0.0f;
+                        nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nj)) : 0u;
+                        col = col + 1 == horizon ? 0 : col + 1;
+                    }
+                }
+                dl4[u] = make_float4(dl[0], dl[1], dl[2], dl[3]);
+                kk4[u] = make_float4(kk[0], kk[1], kk[2], kk[3]);
+                col_g += grp_stride_cols;
+                if (col_g >= horizon) col_g -= horizon;
+            }
+        }
+        __syncthreads();   // every raw operand of the tile has been read
+        float2* const st = reinterpret_cast<float2*>(sd);   // (delta, k) pairs over the d | w region
+#pragma unroll
+        for (int u = 0; u < kB1MaxUnits; ++u) {
+            const int grp = u * kB1Threads + tid;
+            const int e = grp << 2;
+            if (grp < n_grp) {
+                *reinterpret_cast<float4*>(st + e) = make_float4(dl4[u].x, kk4[u].x, dl4[u].y, kk4[u].y);
+                *reinterpret_cast<float4*>(st + e + 2) = make_float4(dl4[u].z, kk4[u].z, dl4[u].w, kk4[u].w);
+            }
+        }
+        const bool any_nonbin = __syncthreads_or((nonbin << 1) != 0u);
+        // ---- 3. chain ----
+        if (tid < 32) {
+            const int lane = tid;
+            const int ro = lane * horizon;
+            const bool mine = lane < rows;
+            float a_run = 0.0f, abs_run = 0.0f;
+            bool literal = any_nonbin;
+            if (!literal) {
+                if (mine) {
+                    int t = horizon - 2;
+                    for (; t >= 7; t -= 8) {   // eight steps' operands first, then the dependent part
+                        float2 p8[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) p8[j] = st[ro + t - j];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            a_run = __fadd_rn(p8[j].x, __fmul_rn(p8[j].y, a_run));
+                            sv[ro + t - j] = a_run;
+                            abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                        }
+                    }
+                    for (; t >= 0; --t) {
+                        const float2 pr = st[ro + t];
+                        a_run = __fadd_rn(pr.x, __fmul_rn(pr.y, a_run));
+                        sv[ro + t] = a_run;
+                        abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                    }
+                }
+                // the running sum of |A| bounds every |A| of the row
+                literal = __any_sync(0xffffffffu, !(abs_run <= 1e30f));
+            }
+            if (literal) {   // rare: the reference's literal order, operands straight from global memory
+                a_run = 0.0f;
+                abs_run = 0.0f;
+                if (mine) {
+                    const long long gro = goff + ro;
+                    for (int t = horizon - 2; t >= 0; --t) {
+                        a_run = adv_step(__ldg(values + gro + t), __ldg(importance + gro + t), __ldg(values + gro + t + 1),
+                                         __ldg(rewards + gro + t + 1), __ldg(dones + gro + t + 1), a_run, gamma, gl,
+                                         rho_clip, c_clip);
+                        sv[ro + t] = a_run;
+                        abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                    }
+                }
+            }
+            if (mine && seg_abs_sum != nullptr) seg_abs_sum[tile * tile_rows + lane] = abs_run;
+        }
+        __syncthreads();
+        // ---- 4. copy-out (advantages are in the v region), column H-1 of every row skipped ----
+        {
+            float* const g = advantages + goff;
+            const int n4 = n_el >> 2;   // the tile starts on a 16-byte boundary
+            int col = (4 * tid) % horizon;
+            for (int e4 = tid; e4 < n4; e4 += kB1Threads) {
+                const int e = e4 << 2;
+                const float4 a4 = *reinterpret_cast<const float4*>(sv + e);
+                if (col + 4 < horizon) {
+                    *reinterpret_cast<float4*>(g + e) = a4;
+                } else {
+                    const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+                    int cj = col;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (cj != horizon - 1) g[e + j] = av[j];
+                        else if (zero_last) g[e + j] = 0.0f;
+                        cj = cj + 1 == horizon ? 0 : cj + 1;
+                    }
+                }
+                col += grp_stride_cols;
+                if (col >= horizon) col -= horizon;
+            }
+            for (int e = (n4 << 2) + tid; e < n_el; e += kB1Threads) {
+                if (e % horizon != horizon - 1) g[e] = sv[e];
+                else if (zero_last) g[e] = 0.0f;
+            }
+        }
+        // the stage is refilled by the async proxy next
+        fence_proxy_async();
+        __syncthreads();
+    }
+    if (failed && tid == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+}
+
+// ---------------------------------------------------------------------------
+// bulk1d, warp-specialised: the odd-horizon counterpart of the tma2d pipeline
+// ---------------------------------------------------------------------------
+// The same split by dependency as puff_adv_tma2d_ws_kernel, on dense tiles of `tile_rows`
+// whole rows (a contiguous span per array, see bulk1d above); eleven warps:
+//   warp 0       producer: four cp.async.bulk copies per tile into a 2-deep ring of raw
+//                stages (plus plain loads of the up to three ragged floats per array)
+//   warps 3..10  terms: stream over the flat tile in units of four elements and write
+//                (delta, k) pairs into one of two terms buffers; afterwards they copy the
+//                finished advantages of the previous tile out to global memory with
+//                coalesced 128-bit stores that skip column H-1
+//   warps 1, 2   chain: warp b owns terms buffer b (every other tile); lane r walks row r
+//                in place, A = delta + k*A stored over k; literal order from global memory
+//                when a non-binary nn was flagged or the advantages near the overflow range
+// One CTA per SM; tiles are pipelined inside it, so the kernel streams at buffer sizes
+// where the one-stage bulk1d kernel is still phase-bound.
+constexpr int kB1wStages = 2;
+constexpr int kB1wTerms = 2;            // terms buffers = chain warps
+constexpr int kB1wTermWarps = 8;
+constexpr int kB1wTermThreads = 32 * kB1wTermWarps;
+constexpr int kB1wThreads = 32 * (1 + kB1wTerms + kB1wTermWarps);
+
+__global__ void __launch_bounds__(kB1wThreads)
+puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
+                          const float* __restrict__ dones, const float* __restrict__ importance,
+                          float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
+                          float lambda, float rho_clip, float c_clip, long long num_segments,
+                          int horizon, int tile_rows, long long num_tiles, int zero_last)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+    uint8_t* const smem_al = smem_raw + (base - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tile_elems = tile_rows * horizon;
+    const uint32_t arr_pitch = (static_cast<uint32_t>(tile_elems) * 4u + 15u) & ~15u;   // one raw array of a stage
+    const uint32_t stage_bytes = 4u * arr_pitch;
+    const uint32_t term_bytes = 2u * arr_pitch;                                          // (delta, k) pairs
+    const uint32_t term_base = kB1wStages * stage_bytes;
+    const uint32_t bar_off = term_base + kB1wTerms * term_bytes;
+    const uint32_t bar_full = base + bar_off;
+    const uint32_t bar_sfree = bar_full + 8 * kB1wStages;
+    const uint32_t bar_tfull = bar_sfree + 8 * kB1wStages;
+    const uint32_t bar_cdone = bar_tfull + 8 * kB1wTerms;
+    const uint32_t flag_base = bar_cdone + 8 * kB1wTerms;
+
+    const long long my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kB1wStages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_sfree + 8 * s, kB1wTermWarps);
+        }
+        for (int b = 0; b < kB1wTerms; ++b) {
+            mbar_init(bar_tfull + 8 * b, kB1wTermWarps);
+            mbar_init(bar_cdone + 8 * b, 1);
+            sts32u(flag_base + 4 * b, 0u);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    const float gl = __fmul_rn(gamma, lambda);
+    bool failed = false;
+    auto rows_of = [&](long long tile) {
+        const long long rem = num_segments - tile * tile_rows;
+        return static_cast<int>(rem < tile_rows ? rem : tile_rows);
+    };
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            const float* const src[4] = {values, rewards, dones, importance};
+            for (long long n = 0; n < my_tiles; ++n) {
+                const int s = static_cast<int>(n % kB1wStages);
+                const uint32_t round = static_cast<uint32_t>(n / kB1wStages);
+                if (round > 0 && !mbar_wait_thread(bar_sfree + 8 * s, (round - 1) & 1u)) {
+                    failed = true;
+                    break;
+                }
+                const long long tile = blockIdx.x + n * gridDim.x;
+                const int n_el = rows_of(tile) * horizon;
+                const long long goff = tile * tile_elems;
+                const uint32_t bulk_bytes = (static_cast<uint32_t>(n_el) * 4u) & ~15u;
+                float* const stage_f = reinterpret_cast<float*>(smem_al + s * stage_bytes);
+                // ragged floats first: the arrive below publishes them together with the bulk bytes
+                for (int e = static_cast<int>(bulk_bytes >> 2); e < n_el; ++e)
+                    for (int a = 0; a < 4; ++a) (stage_f + a * (arr_pitch / 4))[e] = __ldg(src[a] + goff + e);
+                const uint32_t bar = bar_full + 8 * s;
+                if (bulk_bytes != 0u) {
+                    mbar_expect_tx(bar, 4u * bulk_bytes);
+                    for (int a = 0; a < 4; ++a)
+                        bulk_load_1d(base + s * stage_bytes + a * arr_pitch, src[a] + goff, bulk_bytes, bar);
+                } else {
+                    mbar_arrive(bar);
+                }
+            }
+            if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+        }
+    } else if (warp > kB1wTerms) {
+        // --------------------------- terms + copy-out --------------------------
+        const int tt = (warp - 1 - kB1wTerms) * 32 + lane;   // 0 .. kB1wTermThreads-1
+        const int unit_stride_cols = (4 * kB1wTermThreads) % horizon;
+        auto copy_out = [&](long long n) {       // advantages of tile n sit in the .y of its pairs
+            const int b = static_cast<int>(n % kB1wTerms);
+            const long long tile = blockIdx.x + n * gridDim.x;
+            const int n_el = rows_of(tile) * horizon;
+            const float2* const tp = reinterpret_cast<const float2*>(smem_al + term_base + b * term_bytes);
+            float* const g = advantages + tile * tile_elems;
+            // unit by unit, the same units this thread fills in the terms pass: a thread only
+            // ever overwrites pairs whose advantages it has itself written out
+            const int n_grp = (n_el + 3) >> 2;
+            int col = (4 * tt) % horizon;
+            for (int e4 = tt; e4 < n_grp; e4 += kB1wTermThreads) {
+                const int e = e4 << 2;
+                const float4 p0 = *reinterpret_cast<const float4*>(tp + e);
+                const float4 p1 = *reinterpret_cast<const float4*>(tp + e + 2);
+                const float av[4] = {p0.y, p0.w, p1.y, p1.w};
+                if (col + 4 < horizon && e + 4 <= n_el) {
+                    *reinterpret_cast<float4*>(g + e) = make_float4(av[0], av[1], av[2], av[3]);
+                } else {
+                    int cj = col;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (e + j < n_el) {
+                            if (cj != horizon - 1) g[e + j] = av[j];
+                            else if (zero_last) g[e + j] = 0.0f;
+                        }
+                        cj = cj + 1 == horizon ? 0 : cj + 1;
+                    }
+                }
+                col += unit_stride_cols;
+                if (col >= horizon) col -= horizon;
+            }
+        };
+        for (long long n = 0; n < my_tiles; ++n) {
+            const int s = static_cast<int>(n % kB1wStages), b = static_cast<int>(n % kB1wTerms);
+            if (!mbar_wait_warp(bar_full + 8 * s, static_cast<uint32_t>(n / kB1wStages) & 1u)) {
+                failed = true;
+                break;
+            }
+            const long long tile = blockIdx.x + n * gridDim.x;
+            const int n_el = rows_of(tile) * horizon;
+            const int n_grp = (n_el + 3) >> 2;
+            const float* const sv = reinterpret_cast<const float*>(smem_al + s * stage_bytes);
+            const float* const sr = sv + arr_pitch / 4;
+            const float* const sd = sr + arr_pitch / 4;
+            const float* const swt = sd + arr_pitch / 4;
+            float2* const tp = reinterpret_cast<float2*>(smem_al + term_base + b * term_bytes);
+            uint32_t nonbin = 0u;
+            int col_g = (4 * tt) % horizon;
+            for (int grp = tt; grp < n_grp; grp += kB1wTermThreads) {
+                const int e = grp << 2;
+                const float4 v4 = *reinterpret_cast<const float4*>(sv + e);
+                const float4 r4 = *reinterpret_cast<const float4*>(sr + e);
+                const float4 d4 = *reinterpret_cast<const float4*>(sd + e);
+                const float4 w4 = *reinterpret_cast<const float4*>(swt + e);
+                const bool more = e + 4 < n_el;
+                const float v[5] = {v4.x, v4.y, v4.z, v4.w, more ? sv[e + 4] : 0.0f};
+                const float r[5] = {r4.x, r4.y, r4.z, r4.w, more ? sr[e + 4] : 0.0f};
+                const float d[5] = {d4.x, d4.y, d4.z, d4.w, more ? sd[e + 4] : 0.0f};
+                const float w[4] = {w4.x, w4.y, w4.z, w4.w};
+                float dl[4], kk[4];
+                int col = col_g;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const bool valid = (col < horizon - 1) && (e + j < n_el);   // then e+j+1 is in the same row
+                    float dj, gj, nj;
+                    adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
+                    dl[j] = valid ? dj : 0.0f;
+                    kk[j] = valid ? __fmul_rn(gj, nj) : 0.0f;
+                    nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nj)) : 0u;
+                    col = col + 1 == horizon ? 0 : col + 1;
+                }
+                *reinterpret_cast<float4*>(tp + e) = make_float4(dl[0], kk[0], dl[1], kk[1]);
+                *reinterpret_cast<float4*>(tp + e + 2) = make_float4(dl[2], kk[2], dl[3], kk[3]);
+                col_g += unit_stride_cols;
+                if (col_g >= horizon) col_g -= horizon;
+            }
+            if ((nonbin << 1) != 0u) sts32u(flag_base + 4 * b, 1u);
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_tfull + 8 * b);
+                mbar_arrive(bar_sfree + 8 * s);
+            }
+            // the previous tile has been chained meanwhile: write it out
+            if (n > 0) {
+                const int pb = static_cast<int>((n - 1) % kB1wTerms);
+                if (!mbar_wait_warp(bar_cdone + 8 * pb, static_cast<uint32_t>((n - 1) / kB1wTerms) & 1u)) {
+                    failed = true;
+                    break;
+                }
+                copy_out(n - 1);
+            }
+        }
+        if (!failed && my_tiles > 0) {
+            const long long n = my_tiles - 1;
+            if (mbar_wait_warp(bar_cdone + 8 * static_cast<int>(n % kB1wTerms), static_cast<uint32_t>(n / kB1wTerms) & 1u))
+                copy_out(n);
+            else
+                failed = true;
+        }
+        if (failed && lane == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+    } else {
+        // ------------------------------- chain --------------------------------
+        for (long long n = warp - 1; n < my_tiles; n += kB1wTerms) {
+            const int b = warp - 1;
+            if (!mbar_wait_warp(bar_tfull + 8 * b, static_cast<uint32_t>(n / kB1wTerms) & 1u)) {
+                failed = true;
+                break;
+            }
+            const long long tile = blockIdx.x + n * gridDim.x;
+            const int rows = rows_of(tile);
+            float2* const tp = reinterpret_cast<float2*>(smem_al + term_base + b * term_bytes);
+            const uint32_t flag = lds32u(flag_base + 4 * b);
+            __syncwarp();
+            if (lane == 0 && flag != 0u) sts32u(flag_base + 4 * b, 0u);
+            const int ro = lane * horizon;
+            const bool mine = lane < rows;
+            float a_run = 0.0f, abs_run = 0.0f;
+            bool literal = flag != 0u;
+            if (!literal) {
+                if (mine) {
+                    int t = horizon - 2;
+                    for (; t >= 7; t -= 8) {   // eight steps' operands first, then the dependent part
+                        float2 p8[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) p8[j] = tp[ro + t - j];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            a_run = __fadd_rn(p8[j].x, __fmul_rn(p8[j].y, a_run));
+                            tp[ro + t - j].y = a_run;
+                            abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                        }
+                    }
+                    for (; t >= 0; --t) {
+                        const float2 pr = tp[ro + t];
+                        a_run = __fadd_rn(pr.x, __fmul_rn(pr.y, a_run));
+                        tp[ro + t].y = a_run;
+                        abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                    }
+                }
+                literal = __any_sync(0xffffffffu, !(abs_run <= 1e30f));   // the sum bounds every |A| of the row
+            }
+            if (literal) {   // rare: the reference's literal order, operands straight from global memory
+                a_run = 0.0f;
+                abs_run = 0.0f;
+                if (mine) {
+                    const long long gro = tile * tile_elems + ro;
+                    for (int t = horizon - 2; t >= 0; --t) {
+                        a_run = adv_step(__ldg(values + gro + t), __ldg(importance + gro + t), __ldg(values + gro + t + 1),
+                                         __ldg(rewards + gro + t + 1), __ldg(dones + gro + t + 1), a_run, gamma, gl,
+                                         rho_clip, c_clip);
+                        tp[ro + t].y = a_run;
+                        abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                    }
+                }
+            }
+            if (mine && seg_abs_sum != nullptr) seg_abs_sum[tile * tile_rows + lane] = abs_run;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_cdone + 8 * b);
+        }
+        if (failed && lane == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+    }
+}
+
+}  // namespace puff

@@ -1,0 +1,219 @@
+// Affine-pair scan kernel (long rows, few segments) and the generic one-thread-per-row kernel.
+// Included by puff_advantage_sm100.cu after puff_device.cuh.
+#pragma once
+#include "puff_device.cuh"
+
+namespace puff {
+
+// ---------------------------------------------------------------------------
+// scan: NT threads per row, 4 steps per thread, affine-pair scan of the carries
+// ---------------------------------------------------------------------------
+// A_t = delta_t + k_t * A_{t+1} with k_t = ((gamma*lambda)*c_t)*nn_t.  Thread j
+// of a pass owns the unit of four columns G-1-j counted from the end of the
+// row, so the suffix scan in time is an inclusive prefix scan over j.  The
+// composed pair (K, D) of a unit maps the advantage entering it (column 4g+4)
+// to the one leaving it (column 4g): A_out = D + K * A_in.  After the scan each
+// thread knows its own A_in and replays its four steps in the reference's
+// operation order, so only the carry-in differs from the serial result.
+template <bool VEC>
+__global__ void __launch_bounds__(1024)
+puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
+                     const float* __restrict__ dones, const float* __restrict__ importance,
+                     float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
+                     float lambda, float rho_clip, float c_clip, long long num_segments, int horizon,
+                     int zero_last)
+{
+    __shared__ float s_k[32], s_d[32], s_abs[32];
+    __shared__ float s_carry;
+    const int tid = threadIdx.x;
+    const int nt = blockDim.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int nwarps = nt >> 5;
+    const float gl = __fmul_rn(gamma, lambda);
+    const int units = (horizon + 3) >> 2;          // units of 4 columns per row
+    const int passes = (units + nt - 1) / nt;
+
+    for (long long row = blockIdx.x; row < num_segments; row += gridDim.x) {
+        const long long ro = row * horizon;
+        const float* const v = values + ro;
+        const float* const r = rewards + ro;
+        const float* const d = dones + ro;
+        const float* const w = importance + ro;
+        float* const a = advantages + ro;
+        float a_pass = 0.0f;      // advantage entering this pass (from later columns)
+        float abs_acc = 0.0f;     // thread 0 only
+        if (zero_last && tid == 0) a[horizon - 1] = 0.0f;
+
+        for (int p = 0; p < passes; ++p) {
+            const int j = p * nt + tid;
+            const int g = units - 1 - j;
+            const bool live = g >= 0;
+            const int col0 = g << 2;
+            float vv[5], rr[5], dd[5], ww[4];   // index i <-> column col0+i
+#pragma unroll
+            for (int i = 0; i < 5; ++i) {
+                vv[i] = 0.0f;
+                rr[i] = 0.0f;
+                dd[i] = 0.0f;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ww[i] = 0.0f;
+            if (live) {
+                if (VEC) {   // horizon % 4 == 0 and 16-byte aligned bases
+                    const float4 v4 = __ldg(reinterpret_cast<const float4*>(v + col0));
+                    const float4 r4 = __ldg(reinterpret_cast<const float4*>(r + col0));
+                    const float4 d4 = __ldg(reinterpret_cast<const float4*>(d + col0));
+                    const float4 w4 = __ldg(reinterpret_cast<const float4*>(w + col0));
+                    vv[0] = v4.x; vv[1] = v4.y; vv[2] = v4.z; vv[3] = v4.w;
+                    rr[0] = r4.x; rr[1] = r4.y; rr[2] = r4.z; rr[3] = r4.w;
+                    dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
+                    ww[0] = w4.x; ww[1] = w4.y; ww[2] = w4.z; ww[3] = w4.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (col0 + i < horizon) {
+                            vv[i] = __ldg(v + col0 + i);
+                            rr[i] = __ldg(r + col0 + i);
+                            dd[i] = __ldg(d + col0 + i);
+                            ww[i] = __ldg(w + col0 + i);
+                        }
+                    }
+                }
+                if (col0 + 4 < horizon) {
+                    vv[4] = __ldg(v + col0 + 4);
+                    rr[4] = __ldg(r + col0 + 4);
+                    dd[4] = __ldg(d + col0 + 4);
+                }
+            }
+            // local composition over the (up to) four steps, latest column first
+            float K = 1.0f, D = 0.0f;
+            float dl[4], kk[4];
+#pragma unroll
+            for (int i = 3; i >= 0; --i) {
+                const bool step = live && (col0 + i + 1 < horizon);   // t <= H-2
+                const float nn = __fsub_rn(1.0f, dd[i + 1]);
+                const float rho = fminf(ww[i], rho_clip);
+                const float c = fminf(ww[i], c_clip);
+                const float td = __fsub_rn(__fadd_rn(rr[i + 1], __fmul_rn(__fmul_rn(gamma, vv[i + 1]), nn)), vv[i]);
+                dl[i] = step ? __fmul_rn(rho, td) : 0.0f;
+                kk[i] = step ? __fmul_rn(__fmul_rn(gl, c), nn) : 1.0f;
+                D = fmaf(kk[i], D, dl[i]);
+                K = kk[i] * K;
+            }
+            // inclusive prefix scan over j inside the warp
+            float Ki = K, Di = D;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float Kp = __shfl_up_sync(0xffffffffu, Ki, o);
+                const float Dp = __shfl_up_sync(0xffffffffu, Di, o);
+                if (lane >= o) {
+                    Di = fmaf(Ki, Dp, Di);
+                    Ki = Ki * Kp;
+                }
+            }
+            // exclusive prefix inside the warp
+            float Ke = __shfl_up_sync(0xffffffffu, Ki, 1);
+            float De = __shfl_up_sync(0xffffffffu, Di, 1);
+            if (lane == 0) {
+                Ke = 1.0f;
+                De = 0.0f;
+            }
+            float a_in;
+            if (nwarps > 1) {
+                if (lane == 31) {
+                    s_k[warp] = Ki;
+                    s_d[warp] = Di;
+                }
+                __syncthreads();
+                if (warp == 0) {
+                    float Kw = lane < nwarps ? s_k[lane] : 1.0f;
+                    float Dw = lane < nwarps ? s_d[lane] : 0.0f;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const float Kp = __shfl_up_sync(0xffffffffu, Kw, o);
+                        const float Dp = __shfl_up_sync(0xffffffffu, Dw, o);
+                        if (lane >= o) {
+                            Dw = fmaf(Kw, Dp, Dw);
+                            Kw = Kw * Kp;
+                        }
+                    }
+                    // A leaving warp `lane` = Dw + Kw * a_pass: store it, the next warp enters with it
+                    s_d[lane] = fmaf(Kw, a_pass, Dw);
+                }
+                __syncthreads();
+                const float a_warp_in = warp == 0 ? a_pass : s_d[warp - 1];
+                a_in = fmaf(Ke, a_warp_in, De);
+                if (tid == 0) s_carry = s_d[nwarps - 1];
+            } else {
+                a_in = fmaf(Ke, a_pass, De);
+                const float a_out = fmaf(Ki, a_pass, Di);
+                if (tid == 31) s_carry = a_out;
+            }
+            // replay in the reference's operation order
+            float a_run = a_in, abs_loc = 0.0f;
+            float out[4];
+#pragma unroll
+            for (int i = 3; i >= 0; --i) {
+                const bool step = live && (col0 + i + 1 < horizon);
+                if (step) {
+                    a_run = adv_step(vv[i], ww[i], vv[i + 1], rr[i + 1], dd[i + 1], a_run, gamma, gl,
+                                     rho_clip, c_clip);
+                    abs_loc += fabsf(a_run);
+                }
+                out[i] = a_run;
+            }
+            if (live) {
+                if (VEC && col0 + 4 < horizon) {
+                    *reinterpret_cast<float4*>(a + col0) = make_float4(out[0], out[1], out[2], out[3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (col0 + i + 1 < horizon) a[col0 + i] = out[i];
+                }
+            }
+            if (seg_abs_sum != nullptr) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) abs_loc += __shfl_xor_sync(0xffffffffu, abs_loc, o);
+                if (lane == 0) s_abs[warp] = abs_loc;
+            }
+            __syncthreads();   // s_carry, s_abs visible; s_k / s_d reusable
+            a_pass = s_carry;
+            if (seg_abs_sum != nullptr && tid == 0)
+                for (int i = 0; i < nwarps; ++i) abs_acc += s_abs[i];
+            __syncthreads();
+        }
+        if (seg_abs_sum != nullptr && tid == 0) seg_abs_sum[row] = abs_acc;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// generic: serial, one thread per row, plain global loads
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+puff_adv_generic_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
+                        const float* __restrict__ dones, const float* __restrict__ importance,
+                        float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
+                        float lambda, float rho_clip, float c_clip, long long num_segments,
+                        long long horizon, int zero_last)
+{
+    const float gl = __fmul_rn(gamma, lambda);
+    for (long long row = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+         row < num_segments; row += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long ro = row * horizon;
+        float a_run = 0.0f, abs_run = 0.0f;
+        float v_n = __ldg(values + ro + horizon - 1);
+        for (long long t = horizon - 2; t >= 0; --t) {
+            const float v_t = __ldg(values + ro + t);
+            a_run = adv_step(v_t, __ldg(importance + ro + t), v_n, __ldg(rewards + ro + t + 1),
+                             __ldg(dones + ro + t + 1), a_run, gamma, gl, rho_clip, c_clip);
+            abs_run = __fadd_rn(abs_run, fabsf(a_run));
+            advantages[ro + t] = a_run;
+            v_n = v_t;
+        }
+        if (zero_last) advantages[ro + horizon - 1] = 0.0f;
+        if (seg_abs_sum != nullptr) seg_abs_sum[row] = abs_run;
+    }
+}
+
+}  // namespace puff

@@ -1,0 +1,513 @@
+// TMA-tiled serial advantage kernels for H % 4 == 0: single-warp and warp-specialised forms.
+// Included by puff_advantage_sm100.cu after puff_device.cuh.
+#pragma once
+#include "puff_device.cuh"
+
+namespace puff {
+
+// ---------------------------------------------------------------------------
+// tma2d: serial, one warp per CTA, 32-row x 32-column TMA boxes
+// ---------------------------------------------------------------------------
+// Shared memory (offsets from a 1024-byte aligned base, which the 128B swizzle
+// pattern is anchored to):
+//   [0, NST*16K)            NST stages, each v | r | d | w boxes of 4 KB
+//   [NST*16K, NST*16K+8K)   two output boxes (ring for the TMA stores)
+//   then NST mbarriers
+// In a 128B-swizzled box the 16-byte unit q of row r sits at
+// r*128 + ((q ^ (r & 7)) << 4): lane r reading unit q of its own row touches
+// eight different units per quarter-warp, i.e. no bank conflicts.
+template <int NST>
+constexpr int tma2d_smem_bytes()
+{
+    return NST * kStageBytes + 2 * kBoxBytes + NST * 8 + 1024;
+}
+
+template <int NST, bool EPI>
+__global__ void __launch_bounds__(32)
+puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
+                      const __grid_constant__ CUtensorMap tm_r,
+                      const __grid_constant__ CUtensorMap tm_d,
+                      const __grid_constant__ CUtensorMap tm_w,
+                      const __grid_constant__ CUtensorMap tm_a,
+                      const float* adv_in, float* __restrict__ seg_abs_sum, float gamma, float lambda,
+                      float rho_clip, float c_clip, long long num_segments, int horizon, int num_tiles)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t out_base = base + NST * kStageBytes;
+    const uint32_t bar_base = out_base + 2 * kBoxBytes;
+    const int lane = threadIdx.x;
+
+    if (static_cast<int>(blockIdx.x) >= num_tiles) return;
+    const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                         static_cast<int>(gridDim.x);
+    const int nchunks = (horizon + kChunkCols - 1) / kChunkCols;
+    const int total = my_tiles * nchunks;
+
+    if (lane == 0) {
+        prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_r);
+        prefetch_tensormap(&tm_d);
+        prefetch_tensormap(&tm_w);
+        prefetch_tensormap(&tm_a);
+        for (int s = 0; s < NST; ++s) mbar_init(bar_base + 8 * s, 1);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncwarp();
+
+    // work item i -> (tile, chunk); chunks of a tile run from the last column block down
+    auto issue = [&](int i) {
+        const int k = i / nchunks;
+        const int c = nchunks - 1 - (i - k * nchunks);
+        const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+        const int s = i % NST;
+        const uint32_t st = base + s * kStageBytes;
+        const uint32_t bar = bar_base + 8 * s;
+        const int x = c * kChunkCols;
+        const int y = tile * kTileRows;
+        mbar_expect_tx(bar, kStageBytes);
+        tma_load_2d(st + 0 * kBoxBytes, &tm_v, x, y, bar);
+        tma_load_2d(st + 1 * kBoxBytes, &tm_r, x, y, bar);
+        tma_load_2d(st + 2 * kBoxBytes, &tm_d, x, y, bar);
+        tma_load_2d(st + 3 * kBoxBytes, &tm_w, x, y, bar);
+    };
+
+    if (lane == 0) {
+        const int pre = total < NST ? total : NST;
+        for (int i = 0; i < pre; ++i) issue(i);
+    }
+
+    const float gl = __fmul_rn(gamma, lambda);
+    const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
+    const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
+
+    float a_run = 0.0f, abs_run = 0.0f;
+    float nv = 0.0f, nr = 0.0f, nd = 0.0f;   // values/rewards/dones at column t+1 across units
+    float keep_last = 0.0f;                  // the caller's advantages[row, H-1]
+    int k = 0, c = nchunks - 1, s = 0;
+    uint32_t parity = 0;
+    bool failed = false;
+
+    for (int i = 0; i < total; ++i) {
+        if (c == nchunks - 1) {   // new tile
+            const long long row = (static_cast<long long>(blockIdx.x) + static_cast<long long>(k) * gridDim.x) * kTileRows + lane;
+            keep_last = (adv_in != nullptr && row < num_segments) ? adv_in[row * horizon + horizon - 1] : 0.0f;
+            a_run = 0.0f;
+            abs_run = 0.0f;
+        }
+        // the output box i&1 was last read by the store of item i-2
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        if (!mbar_wait_warp(bar_base + 8 * s, parity)) {
+            failed = true;
+            break;
+        }
+        const uint32_t st = base + s * kStageBytes;
+        const uint32_t ob = out_base + (i & 1) * kBoxBytes;
+        const int cbase = c * kChunkCols;
+        float out[32];   // advantages of columns cbase .. cbase+31 of this lane's row
+        const float a_in = a_run, nv_in = nv, nr_in = nr, nd_in = nd;
+        // Full chunks take the packed path; a last chunk that ends inside the box
+        // (H % 32 != 0) and chunks that fail the checks below take the literal one.
+        bool literal = (cbase + kChunkCols > horizon);
+        if (!literal) {
+            literal = !chunk_packed(st, row_off, sw, cbase + kChunkCols == horizon, gamma, gl, rho_clip, c_clip,
+                                    a_run, nv, nr, nd, out);
+        }
+        if (literal) {
+            a_run = a_in;
+            nv = nv_in;
+            nr = nr_in;
+            nd = nd_in;
+            chunk_literal(st, row_off, sw, cbase, horizon, gamma, gl, rho_clip, c_clip, a_run, nv, nr, nd, out);
+        }
+        if (EPI) abs_run = __fadd_rn(abs_run, abs_tree32(out));
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t off = row_off + ((static_cast<uint32_t>(u) ^ sw) << 4);
+            float4 a4 = make_float4(out[4 * u], out[4 * u + 1], out[4 * u + 2], out[4 * u + 3]);
+            // column H-1 (last of its unit, H % 4 == 0) goes back unchanged
+            if (cbase + 4 * u + 3 == horizon - 1) a4.w = keep_last;
+            sts128(ob + off, a4);
+        }
+        const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+        if (EPI && c == 0) {
+            const long long row = static_cast<long long>(tile) * kTileRows + lane;
+            if (row < num_segments) seg_abs_sum[row] = abs_run;
+        }
+        // generic-proxy reads of the stage and writes of the output box are
+        // ordered before the async-proxy operations issued below
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(&tm_a, cbase, tile * kTileRows, ob);
+            bulk_commit();
+            if (i + NST < total) issue(i + NST);
+        }
+        if (--c < 0) {
+            c = nchunks - 1;
+            ++k;
+        }
+        if (++s == NST) {
+            s = 0;
+            parity ^= 1u;
+        }
+    }
+    if (lane == 0) {
+        // the stores only have to be done reading shared memory before the CTA exits;
+        // their global writes complete with the grid
+        bulk_wait_read<0>();
+        if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+    }
+}
+
+
+// ---------------------------------------------------------------------------
+// tma2d, warp-specialised: one CTA per tile stream, six warps with three roles
+// ---------------------------------------------------------------------------
+// A lone warp per tile cannot issue instructions fast enough to keep up with
+// HBM once the pipeline is deep (measured: one such warp per SM is compute
+// bound at about a third of the bandwidth).  Here the work of a 32x32 chunk is
+// split by dependency instead:
+//   warp 0      producer: waits for a free stage, issues the four TMA loads
+//   warps 2..5  terms:    128 threads, 8 columns of one row each, read the raw
+//                         boxes and write delta and k = (gamma*lambda*c)*nn of
+//                         every step into a terms buffer (same swizzled layout);
+//                         columns without a step get delta = k = 0
+//   warp 1      chain:    lane r walks row r's 32 steps from the terms buffer,
+//                         A = delta + k*A, stores the advantages by TMA.  When the
+//                         terms warps flagged a non-binary nn, or A nears the
+//                         overflow range, it redoes the chunk in the reference's
+//                         literal order straight from global memory (rare, slow)
+// Rings: NST raw stages (full: TMA -> terms, sfree: terms -> producer) and NT
+// terms buffers (tfull: terms -> chain, tfree: chain -> terms).
+constexpr int kWsTermWarps = 4;
+constexpr int kWsThreads = 32 * (2 + kWsTermWarps);
+constexpr int kTermBytes = 2 * kBoxBytes;   // delta | k = (gamma*lambda*c)*nn
+
+constexpr int kWsOutSlots = 2;   // output boxes in flight behind the TMA stores
+template <int NST, int NT>
+constexpr int tma2d_ws_smem_bytes()
+{
+    return NST * kStageBytes + NT * kTermBytes + kWsOutSlots * kBoxBytes + (2 * NST + 2 * NT) * 8 + NT * 4 + 64 + 1024;
+}
+
+template <int NST, int NT, bool EPI>
+__global__ void __launch_bounds__(kWsThreads)
+puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
+                         const __grid_constant__ CUtensorMap tm_r,
+                         const __grid_constant__ CUtensorMap tm_d,
+                         const __grid_constant__ CUtensorMap tm_w,
+                         const __grid_constant__ CUtensorMap tm_a,
+                         const float* __restrict__ raw_v, const float* __restrict__ raw_r,
+                         const float* __restrict__ raw_d, const float* __restrict__ raw_w,
+                         const float* adv_in, float* __restrict__ seg_abs_sum, float gamma, float lambda,
+                         float rho_clip, float c_clip, long long num_segments, int horizon, int num_tiles,
+                         int group)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t term_base = base + NST * kStageBytes;
+    const uint32_t out_base = term_base + NT * kTermBytes;
+    const uint32_t bar_full = out_base + kWsOutSlots * kBoxBytes;
+    const uint32_t bar_sfree = bar_full + 8 * NST;
+    const uint32_t bar_tfull = bar_sfree + 8 * NST;
+    const uint32_t bar_tfree = bar_tfull + 8 * NT;
+    const uint32_t flag_base = bar_tfree + 8 * NT;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                         static_cast<int>(gridDim.x);
+    const int nchunks = (horizon + kChunkCols - 1) / kChunkCols;
+    const int total = my_tiles * nchunks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_sfree + 8 * s, kWsTermWarps);
+        }
+        for (int b = 0; b < NT; ++b) {
+            mbar_init(bar_tfull + 8 * b, kWsTermWarps);
+            mbar_init(bar_tfree + 8 * b, 1);
+            sts32u(flag_base + 4 * b, 0u);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    const float gl = __fmul_rn(gamma, lambda);
+    bool failed = false;
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            prefetch_tensormap(&tm_v);
+            prefetch_tensormap(&tm_r);
+            prefetch_tensormap(&tm_d);
+            prefetch_tensormap(&tm_w);
+            // Loads are issued in groups of `group` consecutive chunks (NST % group == 0):
+            // the producer waits until all their stages are free and then issues them back
+            // to back, so that DRAM sees group*128 contiguous bytes of every row at once.
+            int k = 0, c = nchunks - 1, s = 0, round = 0;
+            for (int i = 0; i < total && !failed; i += group) {
+                const int n = total - i < group ? total - i : group;
+                if (round > 0) {
+                    for (int j = 0; j < n; ++j) {
+                        if (!mbar_wait_thread(bar_sfree + 8 * (s + j), static_cast<uint32_t>(round - 1) & 1u)) {
+                            failed = true;
+                            break;
+                        }
+                    }
+                    if (failed) break;
+                }
+                for (int j = 0; j < n; ++j) {
+                    const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+                    const uint32_t st = base + s * kStageBytes;
+                    const uint32_t bar = bar_full + 8 * s;
+                    const int x = c * kChunkCols, y = tile * kTileRows;
+                    mbar_expect_tx(bar, kStageBytes);
+                    tma_load_2d(st + 0 * kBoxBytes, &tm_v, x, y, bar);
+                    tma_load_2d(st + 1 * kBoxBytes, &tm_r, x, y, bar);
+                    tma_load_2d(st + 2 * kBoxBytes, &tm_d, x, y, bar);
+                    tma_load_2d(st + 3 * kBoxBytes, &tm_w, x, y, bar);
+                    if (--c < 0) {
+                        c = nchunks - 1;
+                        ++k;
+                    }
+                    if (++s == NST) {
+                        s = 0;
+                        ++round;
+                    }
+                }
+            }
+            if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+        }
+    } else if (warp >= 2) {
+        // ------------------------------- terms --------------------------------
+        const int tt = (warp - 2) * 32 + lane;   // 0..127
+        const int row = tt >> 2;                  // row of the tile
+        const int g = tt & 3;                     // which 8 columns of the chunk
+        const uint32_t rsw = static_cast<uint32_t>(row) & 7u;
+        const uint32_t off0 = static_cast<uint32_t>(row) * 128u + (((2u * g) ^ rsw) << 4);
+        const uint32_t off1 = static_cast<uint32_t>(row) * 128u + (((2u * g + 1u) ^ rsw) << 4);
+        const uint32_t offn = static_cast<uint32_t>(row) * 128u + ((((2u * g + 2u) & 7u) ^ rsw) << 4);
+        float first_v = 0.0f, first_r = 0.0f, first_d = 0.0f;   // column 0 of the previous (later) chunk
+        int c = nchunks - 1, s = 0, b = 0;
+        uint32_t sround = 0, bround = 0;
+        for (int i = 0; i < total; ++i) {
+            if (c == nchunks - 1) {   // tile start: nothing carries over
+                first_v = 0.0f;
+                first_r = 0.0f;
+                first_d = 0.0f;
+            }
+            if (!mbar_wait_warp(bar_full + 8 * s, sround & 1u)) {
+                failed = true;
+                break;
+            }
+            if (bround > 0 && !mbar_wait_warp(bar_tfree + 8 * b, (bround - 1) & 1u)) {
+                failed = true;
+                break;
+            }
+            const uint32_t st = base + s * kStageBytes;
+            float v[9], r[9], d[9], w[8];
+            {
+                const float4 a0 = lds128(st + 0 * kBoxBytes + off0), a1 = lds128(st + 0 * kBoxBytes + off1);
+                v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+                const float4 b0 = lds128(st + 1 * kBoxBytes + off0), b1 = lds128(st + 1 * kBoxBytes + off1);
+                r[0] = b0.x; r[1] = b0.y; r[2] = b0.z; r[3] = b0.w; r[4] = b1.x; r[5] = b1.y; r[6] = b1.z; r[7] = b1.w;
+                const float4 c0 = lds128(st + 2 * kBoxBytes + off0), c1 = lds128(st + 2 * kBoxBytes + off1);
+                d[0] = c0.x; d[1] = c0.y; d[2] = c0.z; d[3] = c0.w; d[4] = c1.x; d[5] = c1.y; d[6] = c1.z; d[7] = c1.w;
+                const float4 e0 = lds128(st + 3 * kBoxBytes + off0), e1 = lds128(st + 3 * kBoxBytes + off1);
+                w[0] = e0.x; w[1] = e0.y; w[2] = e0.z; w[3] = e0.w; w[4] = e1.x; w[5] = e1.y; w[6] = e1.z; w[7] = e1.w;
+            }
+            // column 8g+8: the next unit of the same row, or (g == 3) the carried column
+            const float nv_s = lds32(st + 0 * kBoxBytes + offn);
+            const float nr_s = lds32(st + 1 * kBoxBytes + offn);
+            const float nd_s = lds32(st + 2 * kBoxBytes + offn);
+            const float nv_c = __shfl_sync(0xffffffffu, first_v, (lane & ~3));
+            const float nr_c = __shfl_sync(0xffffffffu, first_r, (lane & ~3));
+            const float nd_c = __shfl_sync(0xffffffffu, first_d, (lane & ~3));
+            v[8] = g == 3 ? nv_c : nv_s;
+            r[8] = g == 3 ? nr_c : nr_s;
+            d[8] = g == 3 ? nd_c : nd_s;
+            first_v = v[0];
+            first_r = r[0];
+            first_d = d[0];
+            const int col0 = c * kChunkCols + 8 * g;
+            float dl[8], kk[8];
+            uint32_t nonbin = 0u;
+            if (col0 + 8 < horizon) {
+                // all eight columns have a step: the f32x2 forms of the same IEEE operations,
+                // two steps per instruction.  Steps (j, j+1) with odd j take their t+1
+                // operands (j+1, j+2) from aligned register pairs of the 128-bit loads.
+                const float2 neg1 = make_float2(-1.0f, -1.0f), one2 = make_float2(1.0f, 1.0f);
+                const float2 gamma2 = make_float2(gamma, gamma), gl2 = make_float2(gl, gl);
+#pragma unroll
+                for (int j = 1; j < 7; j += 2) {
+                    const float2 dn = make_float2(d[j + 1], d[j + 2]);
+                    const float2 nn2 = __ffma2_rn(dn, neg1, one2);   // 1 - d: exact product, one rounding
+                    const float2 t2 = __fadd2_rn(make_float2(r[j + 1], r[j + 2]),
+                                                 __fmul2_rn(__fmul2_rn(gamma2, make_float2(v[j + 1], v[j + 2])), nn2));
+                    const float2 td2 = make_float2(__fsub_rn(t2.x, v[j]), __fsub_rn(t2.y, v[j + 1]));
+                    const float2 rho2 = make_float2(fminf(w[j], rho_clip), fminf(w[j + 1], rho_clip));
+                    const float2 c2 = make_float2(fminf(w[j], c_clip), fminf(w[j + 1], c_clip));
+                    const float2 d2 = __fmul2_rn(rho2, td2);
+                    const float2 k2 = __fmul2_rn(__fmul2_rn(gl2, c2), nn2);
+                    const float2 q2 = __fmul2_rn(dn, nn2);
+                    nonbin |= __float_as_uint(q2.x) | __float_as_uint(q2.y);
+                    dl[j] = d2.x;
+                    dl[j + 1] = d2.y;
+                    kk[j] = k2.x;
+                    kk[j + 1] = k2.y;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j += 7) {   // steps 0 and 7
+                    float dj, gj, nj;
+                    adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
+                    dl[j] = dj;
+                    kk[j] = __fmul_rn(gj, nj);
+                    nonbin |= __float_as_uint(__fmul_rn(d[j + 1], nj));
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const bool valid = col0 + j < horizon - 1;
+                    float dj, gj, nj;
+                    adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
+                    dl[j] = valid ? dj : 0.0f;
+                    kk[j] = valid ? __fmul_rn(gj, nj) : 0.0f;
+                    nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nj)) : 0u;
+                }
+            }
+            const uint32_t tb = term_base + b * kTermBytes;
+            sts128(tb + 0 * kBoxBytes + off0, make_float4(dl[0], dl[1], dl[2], dl[3]));
+            sts128(tb + 0 * kBoxBytes + off1, make_float4(dl[4], dl[5], dl[6], dl[7]));
+            sts128(tb + 1 * kBoxBytes + off0, make_float4(kk[0], kk[1], kk[2], kk[3]));
+            sts128(tb + 1 * kBoxBytes + off1, make_float4(kk[4], kk[5], kk[6], kk[7]));
+            if ((nonbin << 1) != 0u) sts32u(flag_base + 4 * b, 1u);
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_tfull + 8 * b);
+                mbar_arrive(bar_sfree + 8 * s);
+            }
+            if (--c < 0) c = nchunks - 1;
+            if (++s == NST) {
+                s = 0;
+                ++sround;
+            }
+            if (++b == NT) {
+                b = 0;
+                ++bround;
+            }
+        }
+        if (failed && lane == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+    } else {
+        // ------------------------------- chain --------------------------------
+        if (lane == 0) prefetch_tensormap(&tm_a);
+        const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
+        const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
+        float a_run = 0.0f, abs_run = 0.0f, keep_last = 0.0f;
+        int k = 0, c = nchunks - 1, b = 0, oslot = 0;
+        uint32_t bround = 0;
+        for (int i = 0; i < total; ++i) {
+            const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+            if (c == nchunks - 1) {   // tile start
+                const long long row = static_cast<long long>(tile) * kTileRows + lane;
+                keep_last = (adv_in != nullptr && row < num_segments) ? adv_in[row * horizon + horizon - 1] : 0.0f;
+                a_run = 0.0f;
+                abs_run = 0.0f;
+            }
+            if (!mbar_wait_warp(bar_tfull + 8 * b, bround & 1u)) {
+                failed = true;
+                break;
+            }
+            const uint32_t tb = term_base + b * kTermBytes;
+            float dl[32], kk[32], out[32];
+#pragma unroll
+            for (int u = 7; u >= 0; --u) {
+                const uint32_t off = row_off + ((static_cast<uint32_t>(u) ^ sw) << 4);
+                const float4 x = lds128(tb + 0 * kBoxBytes + off);
+                const float4 y = lds128(tb + 1 * kBoxBytes + off);
+                dl[4 * u] = x.x; dl[4 * u + 1] = x.y; dl[4 * u + 2] = x.z; dl[4 * u + 3] = x.w;
+                kk[4 * u] = y.x; kk[4 * u + 1] = y.y; kk[4 * u + 2] = y.z; kk[4 * u + 3] = y.w;
+            }
+            const uint32_t flag = lds32u(flag_base + 4 * b);
+            // the terms buffer is free as soon as every lane holds its values
+            __syncwarp();
+            if (lane == 0) {
+                if (flag != 0u) sts32u(flag_base + 4 * b, 0u);
+                mbar_arrive(bar_tfree + 8 * b);
+            }
+            const int cbase = c * kChunkCols;
+            const float a_in = a_run;
+            bool literal = flag != 0u;
+            float abs_chunk = 0.0f;
+            if (!literal) {
+#pragma unroll
+                for (int j = 31; j >= 0; --j) {
+                    a_run = __fadd_rn(dl[j], __fmul_rn(kk[j], a_run));
+                    out[j] = a_run;
+                }
+                abs_chunk = abs_tree32(out);
+                literal = __any_sync(0xffffffffu, !(__fadd_rn(fabsf(a_in), abs_chunk) <= 1e30f));
+            }
+            if (literal) {   // rare: the reference's literal order, operands straight from global memory
+                a_run = a_in;
+                const long long row = static_cast<long long>(tile) * kTileRows + lane;
+                const bool in_rows = row < num_segments;
+                const long long ro = (in_rows ? row : 0) * horizon;
+#pragma unroll
+                for (int j = 31; j >= 0; --j) {
+                    const int t = cbase + j;
+                    if (in_rows && t < horizon - 1)
+                        a_run = adv_step(__ldg(raw_v + ro + t), __ldg(raw_w + ro + t), __ldg(raw_v + ro + t + 1),
+                                         __ldg(raw_r + ro + t + 1), __ldg(raw_d + ro + t + 1), a_run, gamma, gl,
+                                         rho_clip, c_clip);
+                    out[j] = a_run;
+                }
+                abs_chunk = abs_tree32(out);
+            }
+            if (EPI) abs_run = __fadd_rn(abs_run, abs_chunk);
+            const uint32_t ob = out_base + oslot * kBoxBytes;
+            if (lane == 0) bulk_wait_read<kWsOutSlots - 1>();   // the store that last used this box has read it
+            __syncwarp();
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t off = row_off + ((static_cast<uint32_t>(u) ^ sw) << 4);
+                float4 a4 = make_float4(out[4 * u], out[4 * u + 1], out[4 * u + 2], out[4 * u + 3]);
+                if (cbase + 4 * u + 3 == horizon - 1) a4.w = keep_last;
+                sts128(ob + off, a4);
+            }
+            if (EPI && c == 0) {
+                const long long row = static_cast<long long>(tile) * kTileRows + lane;
+                if (row < num_segments) seg_abs_sum[row] = abs_run;
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(&tm_a, cbase, tile * kTileRows, ob);
+                bulk_commit();
+            }
+            if (--c < 0) {
+                c = nchunks - 1;
+                ++k;
+            }
+            if (++b == NT) {
+                b = 0;
+                ++bround;
+            }
+            if (++oslot == kWsOutSlots) oslot = 0;
+        }
+        if (lane == 0) {
+            // the stores only have to be done reading shared memory before the CTA exits;
+            // their global writes complete with the grid
+            bulk_wait_read<0>();
+            if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+        }
+    }
+}
+
+}  // namespace puff
