@@ -69,6 +69,11 @@ extern "C" {
  * offsets (cu:48 overflows int at 2^31 elements); num_segments == 0 or
  * horizon < 2 return PUFF_OK without a launch (cu:62 launches a 0-block grid,
  * which is a CUDA error); no allocation, no host synchronisation.
+ *
+ * The first call on each device (from any entry point of this header) queries
+ * the device once and raises the kernels' shared-memory limits; make it during
+ * set-up, before a stream is being captured.  Later calls only encode tensor
+ * maps on the host and launch.
  */
 int puff_advantage_sm100_launch(const float* values, const float* rewards,
                                 const float* dones, const float* importance,

@@ -186,7 +186,7 @@ constexpr int kWsTermWarps = 4;
 constexpr int kWsThreads = 32 * (2 + kWsTermWarps);
 constexpr int kTermBytes = 2 * kBoxBytes;   // delta | k = (gamma*lambda*c)*nn
 
-constexpr int kWsOutSlots = 2;   // output boxes in flight behind the TMA stores
+constexpr int kWsOutSlots = 4;   // output boxes in flight behind the TMA stores (even)
 template <int NST, int NT>
 constexpr int tma2d_ws_smem_bytes()
 {
@@ -472,14 +472,21 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             }
             if (EPI) abs_run = __fadd_rn(abs_run, abs_chunk);
             const uint32_t ob = out_base + oslot * kBoxBytes;
-            if (lane == 0) bulk_wait_read<kWsOutSlots - 1>();   // the store that last used this box has read it
-            __syncwarp();
+            // every second item: once at most kWsOutSlots-2 stores are still reading, the boxes
+            // of this item and the next are free
+            if ((i & 1) == 0) {
+                if (lane == 0) bulk_wait_read<kWsOutSlots - 2>();
+                __syncwarp();
+            }
+            if (cbase + kChunkCols >= horizon) {   // the chunk that holds column H-1: it goes back unchanged
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (cbase + 4 * u + 3 == horizon - 1) out[4 * u + 3] = keep_last;
+            }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const uint32_t off = row_off + ((static_cast<uint32_t>(u) ^ sw) << 4);
-                float4 a4 = make_float4(out[4 * u], out[4 * u + 1], out[4 * u + 2], out[4 * u + 3]);
-                if (cbase + 4 * u + 3 == horizon - 1) a4.w = keep_last;
-                sts128(ob + off, a4);
+                sts128(ob + off, make_float4(out[4 * u], out[4 * u + 1], out[4 * u + 2], out[4 * u + 3]));
             }
             if (EPI && c == 0) {
                 const long long row = static_cast<long long>(tile) * kTileRows + lane;
