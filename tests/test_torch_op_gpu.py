@@ -264,3 +264,63 @@ def test_rollout_write_matches_the_trainer_assignments():
         pufferlib_b200.rollout_write(*bufs, r, d, v, S - 10, 0)       # rows past the end
     with pytest.raises(RuntimeError):
         pufferlib_b200.rollout_write(*bufs, r, d, v, 0, H)            # column past the end
+
+
+def test_op_replays_from_a_cuda_graph():
+    """After one eager call per device the launch path makes no synchronising or
+    allocating call, so the op can be captured and replayed."""
+    import pufferlib_b200
+    for wl in (WORKLOADS["cfg1"], Workload("gws", 20000, 64, seed=3), Workload("godd", 700, 91, seed=4)):
+        host = make_inputs(wl)
+        dev = [t.cuda() for t in host]
+        adv = torch.zeros_like(dev[0])
+        sums = torch.empty(wl.segments, device="cuda")
+        pufferlib_b200.compute_puff_advantage_prio(*dev, adv, sums, *wl.hyper())     # set-up call
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        g = torch.cuda.CUDAGraph()
+        adv.fill_(SENTINEL)
+        with torch.cuda.graph(g, stream=side):
+            pufferlib_b200.compute_puff_advantage_prio(*dev, adv, sums, *wl.hyper())
+        adv.fill_(SENTINEL)
+        sums.fill_(-1)
+        g.replay()
+        torch.cuda.synchronize()
+        want = oracle_advantage([t.numpy() for t in host], wl.hyper())
+        assert bits_equal(adv.cpu().numpy(), want), wl.name
+        exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
+        np.testing.assert_allclose(sums.cpu().numpy(), exact, rtol=1e-5, atol=1e-6)
+
+
+def test_concurrent_launches_from_threads_and_streams():
+    """The launcher is re-entrant: per-thread tensor-map caches, one-time device
+    set-up behind a lock.  Four threads, each on its own stream and buffers."""
+    import threading
+    import pufferlib_b200
+    cases = [Workload(f"t{i}", 3000 + 517 * i, 64 + 32 * (i % 2), seed=40 + i) for i in range(4)]
+    hosts = [make_inputs(wl) for wl in cases]
+    wants = [oracle_advantage([t.numpy() for t in h], wl.hyper()) for h, wl in zip(hosts, cases)]
+    results = [None] * 4
+    errors = []
+
+    def work(i):
+        try:
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                dev = [t.cuda(non_blocking=True) for t in hosts[i]]
+                adv = torch.full_like(dev[0], SENTINEL)
+                for _ in range(20):
+                    pufferlib_b200.compute_puff_advantage(*dev, adv, *cases[i].hyper())
+                results[i] = adv.cpu()
+            st.synchronize()
+        except Exception as exc:   # surfaced below
+            errors.append(exc)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for got, want in zip(results, wants):
+        assert bits_equal(got.numpy(), want)
