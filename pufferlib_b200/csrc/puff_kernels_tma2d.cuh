@@ -45,37 +45,39 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
     const int total = my_tiles * nchunks;
 
     if (lane == 0) {
-        prefetch_tensormap(&tm_v);
-        prefetch_tensormap(&tm_r);
-        prefetch_tensormap(&tm_d);
-        prefetch_tensormap(&tm_w);
-        prefetch_tensormap(&tm_a);
         for (int s = 0; s < NST; ++s) mbar_init(bar_base + 8 * s, 1);
         fence_mbar_init();
         fence_proxy_async();
     }
     __syncwarp();
 
-    // work item i -> (tile, chunk); chunks of a tile run from the last column block down
-    auto issue = [&](int i) {
-        const int k = i / nchunks;
-        const int c = nchunks - 1 - (i - k * nchunks);
-        const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
-        const int s = i % NST;
-        const uint32_t st = base + s * kStageBytes;
-        const uint32_t bar = bar_base + 8 * s;
-        const int x = c * kChunkCols;
+    // work item -> (tile k of this CTA, chunk c); chunks of a tile run from the last column
+    // block down.  The issuing lane keeps its own running (k, c, stage) of the next item to
+    // load, so that nothing but the TMA instructions stands between launch and first bytes.
+    int ld_k = 0, ld_c = nchunks - 1, ld_s = 0, ld_i = 0;
+    auto issue_next = [&]() {
+        const int tile = static_cast<int>(blockIdx.x) + ld_k * static_cast<int>(gridDim.x);
+        const uint32_t st = base + ld_s * kStageBytes;
+        const uint32_t bar = bar_base + 8 * ld_s;
+        const int x = ld_c * kChunkCols;
         const int y = tile * kTileRows;
         mbar_expect_tx(bar, kStageBytes);
         tma_load_2d(st + 0 * kBoxBytes, &tm_v, x, y, bar);
         tma_load_2d(st + 1 * kBoxBytes, &tm_r, x, y, bar);
         tma_load_2d(st + 2 * kBoxBytes, &tm_d, x, y, bar);
         tma_load_2d(st + 3 * kBoxBytes, &tm_w, x, y, bar);
+        if (--ld_c < 0) {
+            ld_c = nchunks - 1;
+            ++ld_k;
+        }
+        if (++ld_s == NST) ld_s = 0;
+        ++ld_i;
     };
 
     if (lane == 0) {
         const int pre = total < NST ? total : NST;
-        for (int i = 0; i < pre; ++i) issue(i);
+        for (int i = 0; i < pre; ++i) issue_next();
+        prefetch_tensormap(&tm_a);
     }
 
     const float gl = __fmul_rn(gamma, lambda);
@@ -143,7 +145,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
         if (lane == 0) {
             tma_store_2d(&tm_a, cbase, tile * kTileRows, ob);
             bulk_commit();
-            if (i + NST < total) issue(i + NST);
+            if (ld_i < total) issue_next();
         }
         if (--c < 0) {
             c = nchunks - 1;
