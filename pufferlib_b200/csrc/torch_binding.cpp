@@ -264,6 +264,23 @@ void compute_puff_advantage_meta(torch::Tensor, torch::Tensor, torch::Tensor, to
                                  double, double, double, double) {}
 void compute_puff_advantage_prio_meta(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor,
                                       torch::Tensor, double, double, double, double) {}
+void compute_puff_advantage_fill_meta(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor,
+                                      std::optional<torch::Tensor>, double, double, double, double) {}
+void puff_rollout_write_meta(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor,
+                             int64_t, int64_t, double) {}
+std::tuple<torch::Tensor, torch::Tensor> puff_priority_weights_meta(torch::Tensor seg_abs_sum, double)
+{
+    return {torch::empty_like(seg_abs_sum), torch::empty({1}, seg_abs_sum.options().dtype(torch::kFloat64))};
+}
+torch::Tensor puff_priority_probs_meta(torch::Tensor weights, torch::Tensor) { return torch::empty_like(weights); }
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor>
+puff_minibatch_gather_meta(torch::Tensor advantages, torch::Tensor, torch::Tensor, torch::Tensor idx, double)
+{
+    const int64_t M = idx.size(0), H = advantages.size(1);
+    const auto o = advantages.options();
+    return {torch::empty({M, H}, o), torch::empty({M, H}, o), torch::empty({M, H}, o), torch::empty({M, H}, o),
+            torch::empty({M, 1}, o)};
+}
 
 TORCH_LIBRARY(pufferlib, m)
 {
@@ -292,6 +309,11 @@ TORCH_LIBRARY_IMPL(pufferlib, Meta, m)
 {
     m.impl("compute_puff_advantage", &compute_puff_advantage_meta);
     m.impl("compute_puff_advantage_prio", &compute_puff_advantage_prio_meta);
+    m.impl("compute_puff_advantage_fill", &compute_puff_advantage_fill_meta);
+    m.impl("puff_rollout_write", &puff_rollout_write_meta);
+    m.impl("puff_priority_weights", &puff_priority_weights_meta);
+    m.impl("puff_priority_probs", &puff_priority_probs_meta);
+    m.impl("puff_minibatch_gather", &puff_minibatch_gather_meta);
 }
 
 }  // namespace pufferlib_b200

@@ -67,3 +67,25 @@ def test_schema_is_the_reference_schema():
     assert schema == ("pufferlib::compute_puff_advantage(Tensor(a!) values, Tensor(b!) rewards, "
                       "Tensor(c!) dones, Tensor(d!) importance, Tensor(e!) advantages, float gamma, "
                       "float lambda, float rho_clip, float c_clip) -> ()")
+
+
+def test_every_op_has_a_shape_kernel():
+    """Meta (shape-only) kernels: the whole minibatch sequence traces without a GPU."""
+    from pufferlib_b200 import _C  # noqa: F401
+    ops = torch.ops.pufferlib
+    S, H, M = 64, 32, 8
+    t = [torch.empty(S, H, device="meta") for _ in range(5)]
+    sums = torch.empty(S, device="meta")
+    ops.compute_puff_advantage(*t, 0.99, 0.95, 1.0, 1.0)
+    ops.compute_puff_advantage_prio(*t, sums, 0.99, 0.95, 1.0, 1.0)
+    ops.compute_puff_advantage_fill(*t, sums, 0.99, 0.95, 1.0, 1.0)
+    ops.compute_puff_advantage_fill(*t, None, 0.99, 0.95, 1.0, 1.0)
+    w, total = ops.puff_priority_weights(sums, 0.8)
+    assert w.shape == (S,) and total.shape == (1,) and total.dtype == torch.float64
+    p = ops.puff_priority_probs(w, total)
+    assert p.shape == (S,)
+    idx = torch.empty(M, dtype=torch.int64, device="meta")
+    out = ops.puff_minibatch_gather(t[4], t[0], p, idx, 0.5)
+    assert [tuple(o.shape) for o in out] == [(M, H)] * 4 + [(M, 1)]
+    step = torch.empty(M, device="meta")
+    ops.puff_rollout_write(t[1], t[2], t[0], step, torch.empty(M, dtype=torch.bool, device="meta"), step, 0, 3, 1.0)
