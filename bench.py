@@ -421,6 +421,9 @@ def run_b200_arm(args, wl, rank, local_rank, world):
     if rank == 0 and not args.no_ref_cuda:
         ref_cuda = time_reference_cuda_kernel(sets, n_sets, hyper, elems)
 
+    # ---- the 9-argument torch op, eager, launch cost included ----------------
+    op_call = time_torch_op(sets, n_sets, hyper, elems) if rank == 0 else None
+
     # ---- end to end through the host-buffer C ABI ----------------------------
     e2e = None
     if args.e2e_steps > 0:
@@ -468,6 +471,7 @@ def run_b200_arm(args, wl, rank, local_rank, world):
                             "gbs_per_gpu": BYTES_PER_ELEMENT * elems / (ko_ms * 1e-3) / 1e9},
             "timing": timing,
             "reference_cuda_kernel": ref_cuda,
+        "torch_op_eager": op_call,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
                          "traffic": TRAFFIC.get((wl.name, kernel_name)) if wl.segments == WORKLOADS[wl.name].segments else None,
@@ -514,6 +518,26 @@ def time_reference_cuda_kernel(sets, n_sets, hyper, elems):
                 "gbs": BYTES_PER_ELEMENT * elems / (ms * 1e-3) / 1e9, "launches": n}
     except Exception as exc:   # the secondary baseline must never break the benchmark
         return {"error": str(exc)[:200]}
+
+
+def time_torch_op(sets, n_sets, hyper, elems):
+    """torch.ops.pufferlib.compute_puff_advantage called eagerly on device
+    tensors (the call of pufferl.py:674): wall clock per call with the Python
+    and dispatcher cost included, device drained before and after the loop."""
+    from pufferlib_b200 import _C  # noqa: F401  (registers the op)
+    op = torch.ops.pufferlib.compute_puff_advantage
+    n = max(50, min(400, 4 * n_sets))
+    for i in range(5):
+        op(*sets[i % n_sets][:5], *hyper)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(n):
+        op(*sets[i % n_sets][:5], *hyper)
+    issue_s = time.perf_counter() - t0
+    torch.cuda.synchronize()
+    wall_s = time.perf_counter() - t0
+    return {"us_per_call": 1e6 * wall_s / n, "host_issue_us_per_call": 1e6 * issue_s / n,
+            "elements_per_s": elems * n / wall_s, "calls": n}
 
 
 def run_sequence_arm(args, wl):

@@ -63,7 +63,7 @@ struct DeviceInfo {
     int cc_major = 0;
     int max_smem_optin = 0;
     cudaError_t err = cudaSuccess;
-    bool ready = false;
+    std::atomic<bool> ready{false};   // set last, with release order, under g_dev_mutex
 };
 static DeviceInfo g_dev[64];
 static std::mutex g_dev_mutex;
@@ -95,14 +95,14 @@ static const DeviceInfo* device_info(int* code)
         return nullptr;
     }
     DeviceInfo& d = g_dev[dev];
-    if (!d.ready) {
+    if (!d.ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(g_dev_mutex);
-        if (!d.ready) {
+        if (!d.ready.load(std::memory_order_relaxed)) {
             cudaError_t e1 = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
             cudaError_t e2 = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
             cudaError_t e3 = cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
             d.err = e1 != cudaSuccess ? e1 : (e2 != cudaSuccess ? e2 : e3);
-            if (d.err == cudaSuccess) {
+            if (d.err == cudaSuccess && d.cc_major == 10) {
                 // opt in to large dynamic shared memory once per device
                 set_tma2d_attrs<2>();
                 set_tma2d_attrs<3>();
@@ -115,12 +115,15 @@ static const DeviceInfo* device_info(int* code)
                 cudaFuncSetAttribute(puff_adv_bulk1d_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem_optin);
                 d.err = cudaGetLastError();
             }
-            d.ready = (d.err == cudaSuccess);
+            // a failed query is retried on the next call; the error is reported from a local
+            // copy so that no other thread reads d.err while it may still change
+            const cudaError_t err = d.err;
+            if (err != cudaSuccess) {
+                *code = static_cast<int>(err);
+                return nullptr;
+            }
+            d.ready.store(true, std::memory_order_release);
         }
-    }
-    if (d.err != cudaSuccess) {
-        *code = static_cast<int>(d.err);
-        return nullptr;
     }
     if (d.cc_major != 10) {
         *code = PUFF_ERR_ARCH;
