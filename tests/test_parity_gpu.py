@@ -161,6 +161,34 @@ def test_small_shape_sweep(force):
             np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6, err_msg=f"S={S} H={H}")
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_random_shapes_and_hyperparameters(seed):
+    """Seeded random shapes (up to a few thousand segments, horizons up to ~1500), clips, discounts
+    and done rates: the automatic choice and every forced serial kernel bit-equal to the oracle."""
+    rng = np.random.default_rng(1234 + seed)
+    for case in range(10):
+        S = int(rng.integers(1, 5000))
+        H = int(rng.choice([rng.integers(2, 48), rng.integers(48, 400), rng.integers(400, 1500)]))
+        if case % 3 == 0:
+            H = (H + 3) // 4 * 4
+        wl = Workload("fuzz", S, H, seed=int(rng.integers(1 << 30)), done_p=float(rng.choice([0.0, 0.01, 0.3, 1.0])),
+                      gamma=float(rng.uniform(0.8, 1.0)), lam=float(rng.uniform(0.0, 1.0)),
+                      rho_clip=float(rng.choice([0.0, 0.5, 1.0, 4.0])), c_clip=float(rng.choice([0.0, 0.9, 1.0, 2.5])),
+                      importance_sigma=float(rng.choice([0.1, 1.0])), value_sigma=float(rng.choice([1.0, 10.0])))
+        inputs = [t.numpy() for t in make_inputs(wl)]
+        want = oracle_advantage(inputs, wl.hyper())
+        exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
+        got, abs_sum, kernel = run_gpu(inputs, wl.hyper(), "serial", None, epilogue=True)
+        assert bits_equal(got, want), f"auto({kernel}) S={S} H={H}: {first_mismatch(got, want)}"
+        np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6)
+        for force, ws in (("tma2d", 0), ("tma2d", 4), ("bulk1d", 0), ("bulk1d", 1), ("generic", None)):
+            if not applicable(force, H):
+                continue
+            got, abs_sum, kernel = run_gpu(inputs, wl.hyper(), "serial", force, epilogue=True, ws=ws)
+            assert bits_equal(got, want), f"{force}/{ws} S={S} H={H} {wl}: {first_mismatch(got, want)}"
+            np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6)
+
+
 @pytest.mark.parametrize("force,H", [("tma2d", 64), ("tma2d", 36), ("bulk1d", 91), ("bulk1d", 30),
                                      ("scan", 64), ("scan", 333), ("generic", 17)])
 def test_canaries_around_buffers(force, H):
