@@ -87,14 +87,23 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
     float a_run = 0.0f, abs_run = 0.0f;
     float nv = 0.0f, nr = 0.0f, nd = 0.0f;   // values/rewards/dones at column t+1 across units
     float keep_last = 0.0f;                  // the caller's advantages[row, H-1]
+    float keep_next = 0.0f;                  // the same for the next tile, fetched one tile ahead
+    if (adv_in != nullptr && my_tiles > 0) {
+        const long long row = static_cast<long long>(blockIdx.x) * kTileRows + lane;
+        if (row < num_segments) keep_next = adv_in[row * horizon + horizon - 1];
+    }
     int k = 0, c = nchunks - 1, s = 0;
     uint32_t parity = 0;
     bool failed = false;
 
     for (int i = 0; i < total; ++i) {
         if (c == nchunks - 1) {   // new tile
-            const long long row = (static_cast<long long>(blockIdx.x) + static_cast<long long>(k) * gridDim.x) * kTileRows + lane;
-            keep_last = (adv_in != nullptr && row < num_segments) ? adv_in[row * horizon + horizon - 1] : 0.0f;
+            keep_last = keep_next;
+            keep_next = 0.0f;
+            if (adv_in != nullptr && k + 1 < my_tiles) {
+                const long long row = (static_cast<long long>(blockIdx.x) + static_cast<long long>(k + 1) * gridDim.x) * kTileRows + lane;
+                if (row < num_segments) keep_next = adv_in[row * horizon + horizon - 1];
+            }
             a_run = 0.0f;
             abs_run = 0.0f;
         }
@@ -412,13 +421,25 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
         const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
         const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
         float a_run = 0.0f, abs_run = 0.0f, keep_last = 0.0f;
+        // The caller's advantages[row, H-1] of a tile is fetched one tile ahead: the value is
+        // needed within the tile's first item, and a DRAM round trip under load is longer than
+        // several items of this warp's work.
+        float keep_next = 0.0f;
+        if (adv_in != nullptr && my_tiles > 0) {
+            const long long row = static_cast<long long>(blockIdx.x) * kTileRows + lane;
+            if (row < num_segments) keep_next = adv_in[row * horizon + horizon - 1];
+        }
         int k = 0, c = nchunks - 1, b = 0, oslot = 0;
         uint32_t bround = 0;
         for (int i = 0; i < total; ++i) {
             const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
             if (c == nchunks - 1) {   // tile start
-                const long long row = static_cast<long long>(tile) * kTileRows + lane;
-                keep_last = (adv_in != nullptr && row < num_segments) ? adv_in[row * horizon + horizon - 1] : 0.0f;
+                keep_last = keep_next;
+                keep_next = 0.0f;
+                if (adv_in != nullptr && k + 1 < my_tiles) {
+                    const long long row = (static_cast<long long>(tile) + gridDim.x) * kTileRows + lane;
+                    if (row < num_segments) keep_next = adv_in[row * horizon + horizon - 1];
+                }
                 a_run = 0.0f;
                 abs_run = 0.0f;
             }
