@@ -394,14 +394,17 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             }
             const long long tiles = (rows + kTileRows - 1) / kTileRows;
             float* abs_p = seg_abs_sum != nullptr ? seg_abs_sum + r0 : nullptr;
-            // Large buffers: the warp-specialised kernel.  Measured on 131072 x 256: four raw
-            // stages whose loads are issued two chunks at a time, two terms buffers, two CTAs
-            // per SM (more CTAs per SM lowered the achieved DRAM rate).  Buffers of only a few
-            // chunks per SM (8192 x 64 and smaller) finish sooner on the single-warp kernel,
-            // whose pipeline has fewer hops.
+            // Large buffers of long rows: the warp-specialised kernel.  Measured on 131072 x 256:
+            // four raw stages whose loads are issued two chunks at a time, two terms buffers,
+            // two CTAs per SM (more CTAs per SM lowered the achieved DRAM rate).  Buffers of
+            // only a few chunks per SM finish sooner on the single-warp kernel, whose pipeline
+            // has fewer hops, and so do rows of at most five chunks at any size (33.5 M
+            // elements: H = 64 112.6 us against 118.8 us, H = 128 110.1 against 110.5,
+            // H = 160 113.0 against 111.1, H = 192 124.9 against 110.1, H = 256 121.2 against 106.3).
             // PUFF_TUNE_WS_STAGES: 0 = single-warp, N = warp-specialised with N raw stages (2, 3, 4, 6).
-            const long long work_items = tiles * ((horizon + kChunkCols - 1) / kChunkCols);
-            const int ws = tune(PUFF_TUNE_WS_STAGES, work_items >= 8LL * dev->sm_count ? 4 : 0);
+            const long long nchunks = (horizon + kChunkCols - 1) / kChunkCols;
+            const long long work_items = tiles * nchunks;
+            const int ws = tune(PUFF_TUNE_WS_STAGES, (work_items >= 8LL * dev->sm_count && nchunks >= 6) ? 4 : 0);
             if (ws != 0) {
                 const int wnst = ws <= 2 ? 2 : ws == 3 ? 3 : ws <= 5 ? 4 : 6;
                 const int smem = wnst * kStageBytes + 2 * kTermBytes + kWsOutSlots * kBoxBytes + 2048;
