@@ -168,9 +168,46 @@ static bool make_map(CUtensorMap* tm, const float* base, long long rows, long lo
 
 struct MapSet {
     const float* ptr[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
-    long long rows = -1, horizon = -1;
     CUtensorMap tm[5];
 };
+
+// Per-thread cache of encoded tensor maps, one entry per (base, rows, horizon).  A map
+// holds nothing but the address and the shape, so an entry stays valid however often the
+// memory behind it is freed and reallocated.  The trainer passes the same four input
+// buffers on every call and a fresh advantages tensor that the caching allocator usually
+// places at the same address: all five lookups hit.
+struct MapEntry {
+    const float* ptr = nullptr;
+    long long rows = -1, horizon = -1;
+    unsigned long long stamp = 0;
+    CUtensorMap tm;
+};
+constexpr int kMapCacheEntries = 16;
+struct MapCache {
+    MapEntry e[kMapCacheEntries];
+    unsigned long long clock = 0;
+};
+
+static const CUtensorMap* cached_map(MapCache& c, const float* base, long long rows, long long horizon)
+{
+    int victim = 0;
+    for (int i = 0; i < kMapCacheEntries; ++i) {
+        MapEntry& m = c.e[i];
+        if (m.ptr == base && m.rows == rows && m.horizon == horizon) {
+            m.stamp = ++c.clock;
+            return &m.tm;
+        }
+        if (m.stamp < c.e[victim].stamp) victim = i;
+    }
+    MapEntry& m = c.e[victim];
+    m.ptr = nullptr;   // not valid while it is being rewritten
+    if (!make_map(&m.tm, base, rows, horizon, horizon)) return nullptr;
+    m.ptr = base;
+    m.rows = rows;
+    m.horizon = horizon;
+    m.stamp = ++c.clock;
+    return &m.tm;
+}
 
 // Tuning knobs (tests, sweeps): process-wide, -1 = automatic.  Initialised once from the
 // environment (PUFF_ADV_FORCE_KERNEL, PUFF_ADV_STAGES, PUFF_ADV_WS, PUFF_ADV_CTAS_PER_SM,
@@ -366,7 +403,8 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
     if (kernel == PUFF_KERNEL_TMA2D) {
         // TMA coordinates are 32-bit: process blocks of at most 2^30 rows
         const long long block_rows = 1LL << 30;
-        static thread_local MapSet cache;
+        static thread_local MapCache map_cache;
+        MapSet cache;
         // measured on cfg2 (131072 x 256): two CTAs per SM with a four-stage ring each
         // beat both more, shallower CTAs and one deeper CTA
         int nst = tune(PUFF_TUNE_STAGES, 4);
@@ -382,15 +420,11 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             const long long rows = num_segments - r0 < block_rows ? num_segments - r0 : block_rows;
             const long long off = r0 * horizon;
             const float* p[5] = {values + off, rewards + off, dones + off, importance + off, advantages + off};
-            bool hit = cache.rows == rows && cache.horizon == horizon;
-            for (int i = 0; i < 5 && hit; ++i) hit = cache.ptr[i] == p[i];
-            if (!hit) {
-                cache.rows = -1;
-                for (int i = 0; i < 5; ++i)
-                    if (!make_map(&cache.tm[i], p[i], rows, horizon, horizon)) return PUFF_ERR_DRIVER;
-                for (int i = 0; i < 5; ++i) cache.ptr[i] = p[i];
-                cache.rows = rows;
-                cache.horizon = horizon;
+            for (int i = 0; i < 5; ++i) {
+                const CUtensorMap* tm = cached_map(map_cache, p[i], rows, horizon);
+                if (tm == nullptr) return PUFF_ERR_DRIVER;
+                cache.tm[i] = *tm;
+                cache.ptr[i] = p[i];
             }
             const long long tiles = (rows + kTileRows - 1) / kTileRows;
             float* abs_p = seg_abs_sum != nullptr ? seg_abs_sum + r0 : nullptr;
