@@ -304,7 +304,6 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
         const uint32_t rsw = static_cast<uint32_t>(row) & 7u;
         const uint32_t off0 = static_cast<uint32_t>(row) * 128u + (((2u * g) ^ rsw) << 4);
         const uint32_t off1 = static_cast<uint32_t>(row) * 128u + (((2u * g + 1u) ^ rsw) << 4);
-        const uint32_t offn = static_cast<uint32_t>(row) * 128u + ((((2u * g + 2u) & 7u) ^ rsw) << 4);
         float first_v = 0.0f, first_r = 0.0f, first_d = 0.0f;   // column 0 of the previous (later) chunk
         int c = nchunks - 1, s = 0, b = 0;
         uint32_t sround = 0, bround = 0;
@@ -334,16 +333,14 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 const float4 e0 = lds128(st + 3 * kBoxBytes + off0), e1 = lds128(st + 3 * kBoxBytes + off1);
                 w[0] = e0.x; w[1] = e0.y; w[2] = e0.z; w[3] = e0.w; w[4] = e1.x; w[5] = e1.y; w[6] = e1.z; w[7] = e1.w;
             }
-            // column 8g+8: the next unit of the same row, or (g == 3) the carried column
-            const float nv_s = lds32(st + 0 * kBoxBytes + offn);
-            const float nr_s = lds32(st + 1 * kBoxBytes + offn);
-            const float nd_s = lds32(st + 2 * kBoxBytes + offn);
-            const float nv_c = __shfl_sync(0xffffffffu, first_v, (lane & ~3));
-            const float nr_c = __shfl_sync(0xffffffffu, first_r, (lane & ~3));
-            const float nd_c = __shfl_sync(0xffffffffu, first_d, (lane & ~3));
-            v[8] = g == 3 ? nv_c : nv_s;
-            r[8] = g == 3 ? nr_c : nr_s;
-            d[8] = g == 3 ? nd_c : nd_s;
+            // column 8g+8: column 0 of the next lane's eight, or (g == 3) column 0 of the
+            // previous (later) chunk, which the row's g == 0 lane carries
+            {
+                const int src = g == 3 ? (lane & ~3) : lane + 1;
+                v[8] = __shfl_sync(0xffffffffu, g == 0 ? first_v : v[0], src);
+                r[8] = __shfl_sync(0xffffffffu, g == 0 ? first_r : r[0], src);
+                d[8] = __shfl_sync(0xffffffffu, g == 0 ? first_d : d[0], src);
+            }
             first_v = v[0];
             first_r = r[0];
             first_d = d[0];
