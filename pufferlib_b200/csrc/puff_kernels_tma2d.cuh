@@ -194,7 +194,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
 // Rings: NST raw stages (full: TMA -> terms, sfree: terms -> producer) and NT
 // terms buffers (tfull: terms -> chain, tfree: chain -> terms).
 constexpr int kWsTermWarps = 4;
-constexpr int kWsThreads = 32 * (2 + kWsTermWarps);
+constexpr int kWsThreads = 32 * (3 + kWsTermWarps);   // warp 5 idles: see the role table
 constexpr int kTermBytes = 2 * kBoxBytes;   // delta | k = (gamma*lambda*c)*nn
 
 constexpr int kWsOutSlots = 4;   // output boxes in flight behind the TMA stores (even)
@@ -296,9 +296,12 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             }
             if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
         }
+    } else if (warp == 5) {
+        // idle: warps are dealt to the SM's four schedulers round robin, so this keeps the
+        // scheduler of the chain warp (warp 1) free of a terms warp
     } else if (warp >= 2) {
         // ------------------------------- terms --------------------------------
-        const int tt = (warp - 2) * 32 + lane;   // 0..127
+        const int tt = (warp == 6 ? 3 : warp - 2) * 32 + lane;   // 0..127
         const int row = tt >> 2;                  // row of the tile
         const int g = tt & 3;                     // which 8 columns of the chunk
         const uint32_t rsw = static_cast<uint32_t>(row) & 7u;
