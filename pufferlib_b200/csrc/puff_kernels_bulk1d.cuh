@@ -266,7 +266,12 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     uint8_t* const smem_al = smem_raw + (base - smem_u32(smem_raw));
-    const int warp = threadIdx.x >> 5;
+    // Logical warp: 0 producer, 1..2 chain, 3..10 terms.  Warps are dealt to the SM's four
+    // schedulers round robin; physical warps 3 and 7 share one that no other warp of the
+    // CTA uses, and the two chain warps get it.
+    const int phys_warp = threadIdx.x >> 5;
+    const int warp = phys_warp == 0 ? 0 : phys_warp == 3 ? 1 : phys_warp == 7 ? 2
+                   : phys_warp < 3 ? phys_warp + 2 : phys_warp < 7 ? phys_warp + 1 : phys_warp;
     const int lane = threadIdx.x & 31;
     const int tile_elems = tile_rows * horizon;
     const uint32_t arr_pitch = (static_cast<uint32_t>(tile_elems) * 4u + 15u) & ~15u;   // one raw array of a stage
