@@ -475,7 +475,7 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
         size_t ws_smem = 0;
         const int ws_rows = bulk1d_ws_tile_rows(horizon, dev->max_smem_optin, &ws_smem);
         // measured at H = 127: the pipeline wins from a few thousand tiles on (131072 rows:
-        // 66 us against 72 us); at 10007 rows the one-stage kernel is ahead (10.6 against 12.5 us)
+        // 65 us against 72 us); at 10007 rows the one-stage kernel is ahead (10.6 against 12.5 us)
         const long long ws_tiles = ws_rows > 0 ? (num_segments + ws_rows - 1) / ws_rows : 0;
         const int use_ws = ws_rows > 0 ? tune(PUFF_TUNE_WS_STAGES, ws_tiles >= 8LL * dev->sm_count ? 1 : 0) : 0;
         if (use_ws != 0) {
