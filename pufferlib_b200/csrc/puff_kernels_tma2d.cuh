@@ -434,6 +434,11 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
         }
         int k = 0, c = nchunks - 1, b = 0, oslot = 0;
         uint32_t bround = 0;
+        // The TMA store of an item is issued one item late, behind the shared-memory loads of
+        // the next item, so that the proxy fence and the store issue overlap their latency.
+        bool pend = false;
+        int pend_x = 0, pend_y = 0;
+        uint32_t pend_ob = 0;
         for (int i = 0; i < total; ++i) {
             const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
             if (c == nchunks - 1) {   // tile start
@@ -461,9 +466,14 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 kk[4 * u] = y.x; kk[4 * u + 1] = y.y; kk[4 * u + 2] = y.z; kk[4 * u + 3] = y.w;
             }
             const uint32_t flag = lds32u(flag_base + 4 * b);
+            if (pend) fence_proxy_async();   // the previous item's output box, written by every lane
             // the terms buffer is free as soon as every lane holds its values
             __syncwarp();
             if (lane == 0) {
+                if (pend) {
+                    tma_store_2d(&tm_a, pend_x, pend_y, pend_ob);
+                    bulk_commit();
+                }
                 if (flag != 0u) sts32u(flag_base + 4 * b, 0u);
                 mbar_arrive(bar_tfree + 8 * b);
             }
@@ -518,12 +528,10 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 const long long row = static_cast<long long>(tile) * kTileRows + lane;
                 if (row < num_segments) seg_abs_sum[row] = abs_run;
             }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
-                tma_store_2d(&tm_a, cbase, tile * kTileRows, ob);
-                bulk_commit();
-            }
+            pend = true;
+            pend_x = cbase;
+            pend_y = tile * kTileRows;
+            pend_ob = ob;
             if (--c < 0) {
                 c = nchunks - 1;
                 ++k;
@@ -533,6 +541,14 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 ++bround;
             }
             if (++oslot == kWsOutSlots) oslot = 0;
+        }
+        if (pend && !failed) {   // the last item's store
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(&tm_a, pend_x, pend_y, pend_ob);
+                bulk_commit();
+            }
         }
         if (lane == 0) {
             // the stores only have to be done reading shared memory before the CTA exits;
