@@ -482,12 +482,19 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             bool literal = flag != 0u;
             float abs_chunk = 0.0f;
             if (!literal) {
+                // sum of |A| on two side chains that issue in the shadow of the recurrence's
+                // dependent multiply-add (fixed order: odd and even columns, then their sum)
+                float s_odd = 0.0f, s_even = 0.0f;
 #pragma unroll
-                for (int j = 31; j >= 0; --j) {
+                for (int j = 31; j >= 0; j -= 2) {
                     a_run = __fadd_rn(dl[j], __fmul_rn(kk[j], a_run));
                     out[j] = a_run;
+                    s_odd = __fadd_rn(s_odd, fabsf(a_run));
+                    a_run = __fadd_rn(dl[j - 1], __fmul_rn(kk[j - 1], a_run));
+                    out[j - 1] = a_run;
+                    s_even = __fadd_rn(s_even, fabsf(a_run));
                 }
-                abs_chunk = abs_tree32(out);
+                abs_chunk = __fadd_rn(s_odd, s_even);
                 literal = __any_sync(0xffffffffu, !(__fadd_rn(fabsf(a_in), abs_chunk) <= 1e30f));
             }
             if (literal) {   // rare: the reference's literal order, operands straight from global memory
