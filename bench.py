@@ -615,7 +615,7 @@ def run_sequence_arm(args, wl):
 # profiles/tma2d_ws_kernel_cfg2_32768x256_ncu_full.md: 138.45 MB read + 15.64 MB written
 # on a 32768-segment case, scaled by the rows of a full launch (every row is read once,
 # so traffic grows in proportion).
-TRAFFIC = {("cfg2", "tma2d"): int((138.45e6 + 16.34e6) * 4)}
+TRAFFIC = {("cfg2", "tma2d"): int((138.45e6 + 14.79e6) * 4)}
 
 
 def main():
