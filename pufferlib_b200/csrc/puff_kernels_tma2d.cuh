@@ -200,7 +200,7 @@ constexpr int kWsTermWarps = 4;
 constexpr int kWsThreads = 32 * (3 + kWsTermWarps);   // warp 5 idles: see the role table
 constexpr int kTermBytes = 2 * kBoxBytes;   // delta | k = (gamma*lambda*c)*nn
 
-constexpr int kWsOutSlots = 4;   // output boxes in flight behind the TMA stores (even)
+constexpr int kWsOutSlots = 4;   // output boxes in flight behind the TMA stores
 template <int NST, int NT>
 constexpr int tma2d_ws_smem_bytes()
 {
@@ -476,6 +476,8 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 }
                 if (flag != 0u) sts32u(flag_base + 4 * b, 0u);
                 mbar_arrive(bar_tfree + 8 * b);
+                // with at most kWsOutSlots-1 stores still reading, this item's output box is free
+                bulk_wait_read<kWsOutSlots - 1>();
             }
             const int cbase = c * kChunkCols;
             const float a_in = a_run;
@@ -515,12 +517,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             }
             if (EPI) abs_run = __fadd_rn(abs_run, abs_chunk);
             const uint32_t ob = out_base + oslot * kBoxBytes;
-            // every second item: once at most kWsOutSlots-2 stores are still reading, the boxes
-            // of this item and the next are free
-            if ((i & 1) == 0) {
-                if (lane == 0) bulk_wait_read<kWsOutSlots - 2>();
-                __syncwarp();
-            }
+            __syncwarp();   // lane 0 has seen this item's output box free (above)
             if (cbase + kChunkCols >= horizon) {   // the chunk that holds column H-1: it goes back unchanged
 #pragma unroll
                 for (int u = 0; u < 8; ++u)
