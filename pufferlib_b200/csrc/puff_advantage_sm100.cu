@@ -428,17 +428,19 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             }
             const long long tiles = (rows + kTileRows - 1) / kTileRows;
             float* abs_p = seg_abs_sum != nullptr ? seg_abs_sum + r0 : nullptr;
-            // Large buffers of long rows: the warp-specialised kernel.  Measured on 131072 x 256:
-            // four raw stages whose loads are issued two chunks at a time, two terms buffers,
-            // two CTAs per SM (more CTAs per SM lowered the achieved DRAM rate).  Buffers of
-            // only a few chunks per SM finish sooner on the single-warp kernel, whose pipeline
-            // has fewer hops, and so do rows of at most five chunks at any size (33.5 M
-            // elements: H = 64 112.6 us against 118.8 us, H = 128 110.1 against 110.5,
-            // H = 160 113.0 against 111.1, H = 192 124.9 against 110.1, H = 256 121.2 against 106.3).
+            // Large buffers: the warp-specialised kernel.  Measured on 131072 x 256: four raw
+            // stages whose loads are issued two chunks at a time, two terms buffers, two CTAs
+            // per SM (more CTAs per SM lowered the achieved DRAM rate).  Buffers of only a few
+            // chunks per SM finish sooner on the single-warp kernel, whose pipeline has fewer
+            // hops, and rows of one or two chunks stay on it at any size (33.5 M elements,
+            // single-warp against warp-specialised: H = 32 128.7 us / 128.9, H = 64 112.4 / 112.4,
+            // H = 96 114.5 / 106.5, H = 128 110.3 / 103.9, H = 160 111.5 / 105.3; at 2-8 M
+            // elements the two are within a few percent from H = 96 on, and the single warp
+            // is 3-5 % ahead at H = 32).
             // PUFF_TUNE_WS_STAGES: 0 = single-warp, N = warp-specialised with N raw stages (2, 3, 4, 6).
             const long long nchunks = (horizon + kChunkCols - 1) / kChunkCols;
             const long long work_items = tiles * nchunks;
-            const int ws = tune(PUFF_TUNE_WS_STAGES, (work_items >= 8LL * dev->sm_count && nchunks >= 6) ? 4 : 0);
+            const int ws = tune(PUFF_TUNE_WS_STAGES, (work_items >= 8LL * dev->sm_count && nchunks >= 3) ? 4 : 0);
             if (ws != 0) {
                 const int wnst = ws <= 2 ? 2 : ws == 3 ? 3 : ws <= 5 ? 4 : 6;
                 const int smem = wnst * kStageBytes + 2 * kTermBytes + kWsOutSlots * kBoxBytes + 2048;
