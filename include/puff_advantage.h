@@ -37,7 +37,9 @@ extern "C" {
 #define PUFF_ERR_SIZE         -10   /* size beyond what the entry point supports  */
 
 /* ---- kernel variants ----------------------------------------------------- */
-#define PUFF_VARIANT_AUTO       0   /* pick from (num_segments, horizon, alignment)            */
+#define PUFF_VARIANT_AUTO       0   /* pick from (num_segments, horizon, alignment): a bit-exact serial kernel,
+                                     * except for few long rows (num_segments < 24 x SM count and horizon >= 512)
+                                     * with gamma*lambda*c_clip <= 1, which take the scan kernel and its error bar */
 #define PUFF_VARIANT_SERIAL     1   /* one thread per row, reference operation order: bit-exact */
 #define PUFF_VARIANT_SCAN       2   /* affine-pair scan along the horizon: |a-b| <= max(1e-6, 1e-5|b|) */
 #define PUFF_VARIANT_GENERIC    3   /* serial, direct global loads; any alignment, any horizon  */

@@ -384,9 +384,15 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
         kernel = can_scan ? PUFF_KERNEL_SCAN : PUFF_KERNEL_GENERIC;
     } else {
         const int serial_kernel = can_tma2d ? PUFF_KERNEL_TMA2D : (can_bulk1d ? PUFF_KERNEL_BULK1D : PUFF_KERNEL_GENERIC);
-        // long rows with too few segments to give every SM a few rows: scan
+        // long rows with too few segments to give every SM a few rows: scan.  Its error bar
+        // rests on a contracting recurrence, so AUTO only takes it while gamma*lambda*c_clip <= 1
+        // (every gain (gamma*lambda)*min(importance, c_clip) is then at most 1); otherwise the
+        // rounding of the re-associated carries could grow along the row, and the bit-exact
+        // serial kernel is used instead.
         const bool few_rows = num_segments < static_cast<long long>(dev->sm_count) * 24;
-        if (variant == PUFF_VARIANT_AUTO && can_scan && few_rows && horizon >= 512)
+        const float gain_cap = gamma * lambda * c_clip;
+        const bool contracting = gain_cap >= 0.0f && gain_cap <= 1.0f;   // false for NaN
+        if (variant == PUFF_VARIANT_AUTO && can_scan && few_rows && horizon >= 512 && contracting)
             kernel = PUFF_KERNEL_SCAN;
         else
             kernel = serial_kernel;

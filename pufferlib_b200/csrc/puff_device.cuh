@@ -18,6 +18,14 @@ constexpr int kTileRows = 32;              // segments per warp tile
 constexpr int kChunkCols = 32;             // columns per TMA box (128 bytes)
 constexpr int kBoxBytes = kTileRows * kChunkCols * 4;   // 4096
 constexpr int kStageBytes = 4 * kBoxBytes;              // v, r, d, w
+// The serial kernels run the chain as A = delta + k*A with k = ((gamma*lambda)*c)*nn, while the
+// reference evaluates (((gamma*lambda)*c)*A)*nn.  For nn in {0, 1} the two agree bit for bit unless
+// the inner product ((gamma*lambda)*c)*A overflows while nn == 0 (the reference then yields
+// inf*0 = NaN, the packed form 0).  A chunk therefore stays on the packed form only while every
+// |(gamma*lambda)*c| <= kPackedMaxGain and every |A| <= kPackedMaxAdv, whose product is below
+// FLT_MAX; anything else is recomputed in the reference's literal order.
+constexpr float kPackedMaxGain = 1e8f;
+constexpr float kPackedMaxAdv = 1e30f;
 constexpr uint32_t kWaitLimit = 1u << 24;             // mbarrier polls before giving up ...
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // ... or two seconds, whichever comes first
 
@@ -267,7 +275,8 @@ __device__ __forceinline__ void chunk_literal(uint32_t st, uint32_t row_off, uin
 // ((gamma*lambda*c)*A)*nn; for nn in {0, 1} that is the same fp32 value as
 // (gamma*lambda*c*nn)*A unless the inner product overflows.  Returns false --
 // and the caller redoes the chunk literally -- when any lane saw d'*nn != 0
-// (nn is not exactly 0 or 1) or advantages beyond 1e30.
+// (nn is not exactly 0 or 1), a gain (gamma*lambda)*c beyond kPackedMaxGain, or advantages
+// beyond kPackedMaxAdv.
 // `row_end`: column cbase+31 is H-1, which has no step.
 __device__ __forceinline__ bool chunk_packed(uint32_t st, uint32_t row_off, uint32_t sw, bool row_end,
                                              float gamma, float gl, float rho_clip, float c_clip,
@@ -295,11 +304,13 @@ __device__ __forceinline__ bool chunk_packed(uint32_t st, uint32_t row_off, uint
 
     float dl[32], kk[32];
     uint32_t nonbin = 0u;
+    float gain = 0.0f;   // largest |(gamma*lambda)*c| of the chunk (a NaN shows up in A instead)
     const float a_in = a_run;
     // step 31 alone (its t+1 operands are the carried ones); masked at the end of a row
     {
         float d, g, n;
         adv_terms(vc[31], wc[31], vc[32], rc[32], dc[32], gamma, gl, rho_clip, c_clip, d, g, n);
+        gain = fmaxf(gain, fabsf(g));
         nonbin |= __float_as_uint(__fmul_rn(dc[32], n));
         dl[31] = row_end ? 0.0f : d;
         kk[31] = row_end ? 0.0f : __fmul_rn(g, n);
@@ -318,8 +329,10 @@ __device__ __forceinline__ bool chunk_packed(uint32_t st, uint32_t row_off, uint
         const float2 rho2 = make_float2(fminf(wc[j], rho_clip), fminf(wc[j + 1], rho_clip));
         const float2 c2 = make_float2(fminf(wc[j], c_clip), fminf(wc[j + 1], c_clip));
         const float2 d2 = __fmul2_rn(rho2, td2);
-        const float2 k2 = __fmul2_rn(__fmul2_rn(gl2, c2), nn2);
+        const float2 g2 = __fmul2_rn(gl2, c2);
+        const float2 k2 = __fmul2_rn(g2, nn2);
         const float2 q2 = __fmul2_rn(dn, nn2);
+        gain = fmaxf(gain, fmaxf(fabsf(g2.x), fabsf(g2.y)));
         nonbin |= __float_as_uint(q2.x) | __float_as_uint(q2.y);
         dl[j] = d2.x;
         dl[j + 1] = d2.y;
@@ -329,6 +342,7 @@ __device__ __forceinline__ bool chunk_packed(uint32_t st, uint32_t row_off, uint
     {
         float d, g, n;
         adv_terms(vc[0], wc[0], vc[1], rc[1], dc[1], gamma, gl, rho_clip, c_clip, d, g, n);
+        gain = fmaxf(gain, fabsf(g));
         nonbin |= __float_as_uint(__fmul_rn(dc[1], n));
         dl[0] = d;
         kk[0] = __fmul_rn(g, n);
@@ -342,7 +356,7 @@ __device__ __forceinline__ bool chunk_packed(uint32_t st, uint32_t row_off, uint
     }
     a_run = a;
     const float big = __fadd_rn(fabsf(a_in), abs_tree32(out));
-    const bool ok = ((nonbin << 1) == 0u) && (big <= 1e30f);
+    const bool ok = ((nonbin << 1) == 0u) && (big <= kPackedMaxAdv) && (gain <= kPackedMaxGain);
     return __all_sync(0xffffffffu, ok);
 }
 

@@ -97,6 +97,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
         // a thread owns units of four consecutive elements (one 16-byte unit per array);
         // the operand at e+4 comes from the next unit
         uint32_t nonbin = 0u;
+        float gain = 0.0f;   // largest |(gamma*lambda)*c| of this thread's steps
         const int n_grp = (n_el + 3) >> 2;
         const int grp_stride_cols = (4 * kB1Threads) % horizon;
         float4 dl4[kB1MaxUnits], kk4[kB1MaxUnits];
@@ -129,6 +130,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                         adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
                         dl[j] = valid ? dj : 0.0f;
                         kk[j] = valid ? __fmul_rn(gj, nj) : 0.0f;
+                        gain = valid ? fmaxf(gain, fabsf(gj)) : gain;
                         nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nj)) : 0u;
                         col = col + 1 == horizon ? 0 : col + 1;
                     }
@@ -150,7 +152,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                 *reinterpret_cast<float4*>(st + e + 2) = make_float4(dl4[u].z, kk4[u].z, dl4[u].w, kk4[u].w);
             }
         }
-        const bool any_nonbin = __syncthreads_or((nonbin << 1) != 0u);
+        const bool any_nonbin = __syncthreads_or((nonbin << 1) != 0u || !(gain <= kPackedMaxGain));
         // ---- 3. chain ----
         if (tid < 32) {
             const int lane = tid;
@@ -180,7 +182,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                     }
                 }
                 // the running sum of |A| bounds every |A| of the row
-                literal = __any_sync(0xffffffffu, !(abs_run <= 1e30f));
+                literal = __any_sync(0xffffffffu, !(abs_run <= kPackedMaxAdv));
             }
             if (literal) {   // rare: the reference's literal order, operands straight from global memory
                 a_run = 0.0f;
@@ -389,6 +391,7 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
             const float* const swt = sd + arr_pitch / 4;
             float2* const tp = reinterpret_cast<float2*>(smem_al + term_base + b * term_bytes);
             uint32_t nonbin = 0u;
+            float gain = 0.0f;   // largest |(gamma*lambda)*c| of this thread's steps
             int col_g = (4 * tt) % horizon;
             for (int grp = tt; grp < n_grp; grp += kB1wTermThreads) {
                 const int e = grp << 2;
@@ -410,6 +413,7 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                     adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
                     dl[j] = valid ? dj : 0.0f;
                     kk[j] = valid ? __fmul_rn(gj, nj) : 0.0f;
+                    gain = valid ? fmaxf(gain, fabsf(gj)) : gain;
                     nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nj)) : 0u;
                     col = col + 1 == horizon ? 0 : col + 1;
                 }
@@ -418,7 +422,7 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                 col_g += unit_stride_cols;
                 if (col_g >= horizon) col_g -= horizon;
             }
-            if ((nonbin << 1) != 0u) sts32u(flag_base + 4 * b, 1u);
+            if ((nonbin << 1) != 0u || !(gain <= kPackedMaxGain)) sts32u(flag_base + 4 * b, 1u);
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(bar_tfull + 8 * b);
@@ -481,7 +485,7 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                         abs_run = __fadd_rn(abs_run, fabsf(a_run));
                     }
                 }
-                literal = __any_sync(0xffffffffu, !(abs_run <= 1e30f));   // the sum bounds every |A| of the row
+                literal = __any_sync(0xffffffffu, !(abs_run <= kPackedMaxAdv));   // the sum bounds every |A| of the row
             }
             if (literal) {   // rare: the reference's literal order, operands straight from global memory
                 a_run = 0.0f;

@@ -43,6 +43,8 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
         float* const a = advantages + ro;
         float a_pass = 0.0f;      // advantage entering this pass (from later columns)
         float abs_acc = 0.0f;     // thread 0 only
+        float gain = 0.0f;        // largest |(gamma*lambda)*c| of this thread's steps
+        float chk = 0.0f;         // sum of this thread's |A|: inf or NaN as soon as one of them is
         if (zero_last && tid == 0) a[horizon - 1] = 0.0f;
 
         for (int p = 0; p < passes; ++p) {
@@ -96,8 +98,10 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
                 const float rho = fminf(ww[i], rho_clip);
                 const float c = fminf(ww[i], c_clip);
                 const float td = __fsub_rn(__fadd_rn(rr[i + 1], __fmul_rn(__fmul_rn(gamma, vv[i + 1]), nn)), vv[i]);
+                const float gc = __fmul_rn(gl, c);
                 dl[i] = step ? __fmul_rn(rho, td) : 0.0f;
-                kk[i] = step ? __fmul_rn(__fmul_rn(gl, c), nn) : 1.0f;
+                kk[i] = step ? __fmul_rn(gc, nn) : 1.0f;
+                gain = step ? fmaxf(gain, fabsf(gc)) : gain;
                 D = fmaf(kk[i], D, dl[i]);
                 K = kk[i] * K;
             }
@@ -152,6 +156,7 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
             }
             // replay in the reference's operation order
             float a_run = a_in, abs_loc = 0.0f;
+            chk += fabsf(a_in);
             float out[4];
 #pragma unroll
             for (int i = 3; i >= 0; --i) {
@@ -182,6 +187,23 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
             if (seg_abs_sum != nullptr && tid == 0)
                 for (int i = 0; i < nwarps; ++i) abs_acc += s_abs[i];
             __syncthreads();
+            chk += abs_loc;   // after the warp reduction: lane sums, still inf / NaN when any |A| is
+        }
+        // Folding nn into k changes the result (not just its rounding) when ((gamma*lambda)*c)*A
+        // overflows under nn == 0: the reference then carries NaN to the start of the row.  A row
+        // with a gain beyond kPackedMaxGain or an advantage beyond kPackedMaxAdv is redone by one
+        // thread in the reference's literal order (rare, slow).
+        if (__syncthreads_or(!(gain <= kPackedMaxGain) || !(chk <= kPackedMaxAdv))) {
+            if (tid == 0) {
+                float a_run = 0.0f, abs_run = 0.0f;
+                for (int t = horizon - 2; t >= 0; --t) {
+                    a_run = adv_step(__ldg(v + t), __ldg(w + t), __ldg(v + t + 1), __ldg(r + t + 1), __ldg(d + t + 1),
+                                     a_run, gamma, gl, rho_clip, c_clip);
+                    abs_run = __fadd_rn(abs_run, fabsf(a_run));
+                    a[t] = a_run;
+                }
+                abs_acc = abs_run;
+            }
         }
         if (seg_abs_sum != nullptr && tid == 0) seg_abs_sum[row] = abs_acc;
     }

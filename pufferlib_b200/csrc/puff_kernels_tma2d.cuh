@@ -188,9 +188,10 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
 //                         columns without a step get delta = k = 0
 //   warp 1      chain:    lane r walks row r's 32 steps from the terms buffer,
 //                         A = delta + k*A, stores the advantages by TMA.  When the
-//                         terms warps flagged a non-binary nn, or A nears the
-//                         overflow range, it redoes the chunk in the reference's
-//                         literal order straight from global memory (rare, slow)
+//                         terms warps flagged a non-binary nn or a gain beyond
+//                         kPackedMaxGain, or A exceeds kPackedMaxAdv, it redoes the
+//                         chunk in the reference's literal order straight from global
+//                         memory (rare, slow)
 //   warp 5      idle:     warps are dealt to the SM's four schedulers round robin, so
 //                         an idle warp 5 leaves the scheduler of warp 1 to the chain
 //                         warps of the SM's two CTAs (measured 1.6 % faster)
@@ -353,6 +354,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             const int col0 = c * kChunkCols + 8 * g;
             float dl[8], kk[8];
             uint32_t nonbin = 0u;
+            float gain = 0.0f;   // largest |(gamma*lambda)*c| of this thread's steps
             if (col0 + 8 < horizon) {
                 // all eight columns have a step: the f32x2 forms of the same IEEE operations,
                 // two steps per instruction.  Steps (j, j+1) with odd j take their t+1
@@ -369,8 +371,10 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                     const float2 rho2 = make_float2(fminf(w[j], rho_clip), fminf(w[j + 1], rho_clip));
                     const float2 c2 = make_float2(fminf(w[j], c_clip), fminf(w[j + 1], c_clip));
                     const float2 d2 = __fmul2_rn(rho2, td2);
-                    const float2 k2 = __fmul2_rn(__fmul2_rn(gl2, c2), nn2);
+                    const float2 g2 = __fmul2_rn(gl2, c2);
+                    const float2 k2 = __fmul2_rn(g2, nn2);
                     const float2 q2 = __fmul2_rn(dn, nn2);
+                    gain = fmaxf(gain, fmaxf(fabsf(g2.x), fabsf(g2.y)));
                     nonbin |= __float_as_uint(q2.x) | __float_as_uint(q2.y);
                     dl[j] = d2.x;
                     dl[j + 1] = d2.y;
@@ -383,6 +387,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                     adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
                     dl[j] = dj;
                     kk[j] = __fmul_rn(gj, nj);
+                    gain = fmaxf(gain, fabsf(gj));
                     nonbin |= __float_as_uint(__fmul_rn(d[j + 1], nj));
                 }
             } else {
@@ -393,6 +398,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                     adv_terms(v[j], w[j], v[j + 1], r[j + 1], d[j + 1], gamma, gl, rho_clip, c_clip, dj, gj, nj);
                     dl[j] = valid ? dj : 0.0f;
                     kk[j] = valid ? __fmul_rn(gj, nj) : 0.0f;
+                    gain = valid ? fmaxf(gain, fabsf(gj)) : gain;
                     nonbin |= valid ? __float_as_uint(__fmul_rn(d[j + 1], nj)) : 0u;
                 }
             }
@@ -401,7 +407,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             sts128(tb + 0 * kBoxBytes + off1, make_float4(dl[4], dl[5], dl[6], dl[7]));
             sts128(tb + 1 * kBoxBytes + off0, make_float4(kk[0], kk[1], kk[2], kk[3]));
             sts128(tb + 1 * kBoxBytes + off1, make_float4(kk[4], kk[5], kk[6], kk[7]));
-            if ((nonbin << 1) != 0u) sts32u(flag_base + 4 * b, 1u);
+            if ((nonbin << 1) != 0u || !(gain <= kPackedMaxGain)) sts32u(flag_base + 4 * b, 1u);
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(bar_tfull + 8 * b);
@@ -497,7 +503,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                     s_even = __fadd_rn(s_even, fabsf(a_run));
                 }
                 abs_chunk = __fadd_rn(s_odd, s_even);
-                literal = __any_sync(0xffffffffu, !(__fadd_rn(fabsf(a_in), abs_chunk) <= 1e30f));
+                literal = __any_sync(0xffffffffu, !(__fadd_rn(fabsf(a_in), abs_chunk) <= kPackedMaxAdv));
             }
             if (literal) {   // rare: the reference's literal order, operands straight from global memory
                 a_run = a_in;

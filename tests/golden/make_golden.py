@@ -84,6 +84,26 @@ def main():
         arrays[f"special.{key}"] = t.numpy()
     arrays["special.advantages"] = adv.numpy()
     meta["special"] = {"hyper": list(wl.hyper()), "segments": 12, "horizon": 40}
+    # ((gamma*lambda)*c)*A overflows to inf while nn == 0: the reference then carries inf*0 = NaN
+    # to the start of the row, whereas (((gamma*lambda)*c)*nn)*A would be 0.  Rows 0..15 get there
+    # through a huge clip and ratio (c = 1e12 against A ~ 1e29), rows 16..31 through a hugely
+    # negative ratio (c = min(w, c_clip) = -1e30 against A ~ 1e10); the rest stay finite.
+    wl = Workload("gain_overflow", 48, 96, seed=13, done_p=0.05, rho_clip=1.0, c_clip=1e12)
+    v, r, d, w = make_inputs(wl)
+    r[0:16, 70] = 1e29
+    d[0:16, 70] = 0.0
+    d[0:16, 69] = 1.0
+    w[0:16, 68] = 1e12
+    r[16:32, 40] = 1e10
+    d[16:32, 40] = 0.0
+    d[16:32, 39] = 1.0
+    w[16:32, 38] = -1e30
+    adv = run_reference(ref, (v, r, d, w), wl.hyper())
+    assert torch.isnan(adv[0:32, 0]).all() and torch.isfinite(adv[32:, :-1]).all()
+    for key, t in zip(("values", "rewards", "dones", "importance"), (v, r, d, w)):
+        arrays[f"gain_overflow.{key}"] = t.numpy()
+    arrays["gain_overflow.advantages"] = adv.numpy()
+    meta["gain_overflow"] = {"hyper": list(wl.hyper()), "segments": 48, "horizon": 96}
     arrays["meta"] = np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8)
     np.savez_compressed(os.path.join(out_dir, "small_cases.npz"), **arrays)
 

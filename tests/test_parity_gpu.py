@@ -69,22 +69,39 @@ def test_serial_kernels_match_golden_bitwise(golden_small, force):
 
 def test_scan_kernel_matches_golden_within_tolerance(golden_small):
     for name, case in golden_small.items():
-        if name in ("special", "odd127"):
-            continue   # non-finite inputs / |values| ~ 10: outside the scan variant's stated bar
+        if name in ("special", "odd127", "gain_overflow"):
+            continue   # non-finite values / |values| ~ 10: outside the scan variant's stated bar
         got, _, kernel = run_gpu([case[k] for k in KEYS], case["hyper"], "scan")
         want = case["advantages"]
         assert np.all(got[:, -1] == np.float32(SENTINEL)), name
         assert within_scan_tolerance(got[:, :-1], want[:, :-1]), name
 
 
-def test_scan_special_values_propagate(golden_small):
-    """NaN / Inf positions agree with the reference even where values differ in rounding."""
-    case = golden_small["special"]
-    got, _, _ = run_gpu([case[k] for k in KEYS], case["hyper"], "scan")
+@pytest.mark.parametrize("name", ["special", "gain_overflow"])
+def test_scan_special_values_propagate(golden_small, name):
+    """NaN / Inf positions agree with the reference even where values differ in
+    rounding; a row whose ((gamma*lambda)*c)*A overflows under nn == 0 is NaN
+    from there to its start, as in the reference."""
+    case = golden_small[name]
+    got, _, kernel = run_gpu([case[k] for k in KEYS], case["hyper"], "scan")
+    assert kernel == "scan"
     want = case["advantages"]
     assert np.array_equal(np.isnan(got), np.isnan(want))
     fin = np.isfinite(want)
     np.testing.assert_allclose(got[fin], want[fin], rtol=1e-4, atol=1e-5)
+
+
+def test_auto_keeps_serial_kernel_when_gain_can_exceed_one():
+    """Few long rows take the scan kernel under AUTO only while
+    gamma*lambda*c_clip <= 1; otherwise AUTO stays bit-exact."""
+    wl = Workload("fewlong", 64, 1024, seed=31, c_clip=3.0, importance_sigma=1.0)
+    inputs = [t.numpy() for t in make_inputs(wl)]
+    got, _, kernel = run_gpu(inputs, wl.hyper(), "auto")
+    assert kernel == "tma2d"
+    want = oracle_advantage(inputs, wl.hyper())
+    assert bits_equal(got, want), first_mismatch(got, want)
+    _, _, kernel = run_gpu(inputs, (0.99, 0.95, 1.0, 1.0), "auto")
+    assert kernel == "scan"
 
 
 # ---------------------------------------------------------------------------
@@ -313,6 +330,42 @@ def test_products_near_overflow_follow_the_reference_order():
     for force in ("tma2d", "bulk1d", "generic"):
         got, _, _ = run_gpu([v, r, d, w], hyper, "serial", force)
         assert bits_equal(got, want), (force, first_mismatch(got, want))
+
+
+@pytest.mark.parametrize("H", [64, 256, 127])
+def test_huge_gain_overflow_follows_the_reference_order(H):
+    """The same overflow reached through the gain instead of the advantage:
+    c = min(w, c_clip) = 1e12 (or a hugely negative ratio) against a moderate
+    A.  Enough rows that every kernel form is exercised, with and without the
+    warp-specialised pipeline."""
+    S = 6000
+    rng = np.random.default_rng(17)
+    v = rng.standard_normal((S, H)).astype(np.float32)
+    r = (0.1 * rng.standard_normal((S, H))).astype(np.float32)
+    d = (rng.random((S, H)) < 0.05).astype(np.float32)
+    w = np.exp(0.3 * rng.standard_normal((S, H))).astype(np.float32)
+    rows = np.arange(0, S, 7)
+    t0 = H - 10
+    r[rows, t0 + 1] = 1e29
+    d[rows, t0 + 1] = 0.0
+    d[rows, t0] = 1.0
+    w[rows, t0 - 1] = 1e12
+    rows2 = np.arange(3, S, 11)
+    r[rows2, 21] = 1e10
+    d[rows2, 21] = 0.0
+    d[rows2, 20] = 1.0
+    w[rows2, 19] = -1e30
+    hyper = (0.99, 0.95, 1.0, 1e12)
+    want = oracle_advantage([v, r, d, w], hyper)
+    assert np.isnan(want[rows, 0]).all() and np.isnan(want[rows2, 0]).all()
+    for force, ws in (("tma2d", 0), ("tma2d", 4), ("bulk1d", 0), ("bulk1d", 1), ("generic", None)):
+        if not applicable(force, H):
+            continue
+        got, _, kernel = run_gpu([v, r, d, w], hyper, "serial", force, ws=ws)
+        assert kernel == force
+        assert bits_equal(got, want), (force, ws, first_mismatch(got, want))
+    got, _, _ = run_gpu([v, r, d, w], hyper, "scan")
+    assert np.array_equal(np.isnan(got), np.isnan(want))
 
 
 def test_non_binary_dones_are_used_arithmetically():
