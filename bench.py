@@ -280,7 +280,7 @@ def run_b200_arm(args, wl, rank, local_rank, world):
         sets.append(ins + [torch.zeros((S, H), device=dev), tuple(torch.empty(S, device=dev) for _ in range(DEPTH))])
     sharded = ShardedAdvantage(S * world, H, hyper, PRIO_ALPHA, rank=rank, world=world)
     variant = args.variant
-    os.environ["PUFFER_ADV_VARIANT"] = variant
+    pufferlib_b200.set_variant(variant)
     side_stream = torch.cuda.Stream(priority=-1)
     pending = collections.deque()
     last = {}

@@ -72,6 +72,13 @@ extern "C" {
  * horizon < 2 return PUFF_OK without a launch (cu:62 launches a 0-block grid,
  * which is a CUDA error); no allocation, no host synchronisation.
  *
+ * Every wait inside the kernels is bounded.  A wait that gives up records
+ * PUFF_ERR_DEVICE_WAIT in a per-device status word and the kernel returns with
+ * part of the output unwritten; this asynchronous entry point cannot report
+ * that.  A caller that needs to know polls puff_advantage_sm100_device_status
+ * at its own synchronisation points (the synchronous _host entry point does it
+ * itself and returns the code).
+ *
  * The first call on each device (from any entry point of this header) queries
  * the device once and raises the kernels' shared-memory limits; make it during
  * set-up, before a stream is being captured.  Later calls only encode tensor
@@ -113,6 +120,8 @@ int puff_advantage_sm100_launch_ex(const float* values, const float* rewards,
  * h_advantages[:, horizon-1] is left untouched.  The device staging workspace
  * is allocated on first use and cached per device; puff_advantage_sm100_host_release
  * frees it.  Bytes moved: 16*S*H host->device, 4*S*(H-1) (+4*S) device->host.
+ * Returns PUFF_ERR_DEVICE_WAIT (and clears the status word) when a bounded wait
+ * inside one of its kernels gave up: the output is then incomplete.
  */
 int puff_advantage_sm100_host(const float* h_values, const float* h_rewards,
                               const float* h_dones, const float* h_importance,
@@ -157,10 +166,17 @@ int puff_priorities_sm100_probs(const float* weights, const double* total_w,
  *     mb_adv_norm = mb_prio[:, None] * (mb_adv_raw - mean) / (std + 1e-8)
  * with mean and the unbiased std taken over all gathered elements (fp64
  * accumulation through `scratch`, fixed order).  idx is int64 on the device; an
- * index outside [0, num_segments) yields zero rows and raises the flag that
+ * index outside [0, num_segments) yields zero rows in all four outputs and
+ * mb_prio = 0 (its zeros still count in mean and std), and raises the flag that
  * puff_minibatch_sm100_bad_index() returns (and clears) after synchronising.
  * scratch: at least puff_minibatch_sm100_scratch_bytes(mb_segments) bytes,
  * 8-byte aligned, caller-owned.
+ *
+ * _gather_ex takes the N of `(N * prio_probs[idx]) ** -beta` separately, as
+ * prio_segments >= num_segments: a caller whose segments are sharded over
+ * several GPUs passes its local rows as num_segments (the bound of idx) and
+ * the global segment count, over which prio_probs was normalised, as
+ * prio_segments.  _gather is _gather_ex with prio_segments = num_segments.
  */
 size_t puff_minibatch_sm100_scratch_bytes(long long mb_segments);
 int puff_minibatch_sm100_gather(const float* advantages, const float* values,
@@ -170,6 +186,13 @@ int puff_minibatch_sm100_gather(const float* advantages, const float* values,
                                 long long num_segments, long long horizon,
                                 long long mb_segments, void* scratch, size_t scratch_bytes,
                                 void* cuda_stream);
+int puff_minibatch_sm100_gather_ex(const float* advantages, const float* values,
+                                   const float* prio_probs, const long long* idx,
+                                   float* mb_values, float* mb_returns, float* mb_adv_raw,
+                                   float* mb_adv_norm, float* mb_prio, float anneal_beta,
+                                   long long num_segments, long long prio_segments,
+                                   long long horizon, long long mb_segments,
+                                   void* scratch, size_t scratch_bytes, void* cuda_stream);
 int puff_minibatch_sm100_bad_index(void);
 
 /*
@@ -229,8 +252,14 @@ int puff_advantage_sm100_last_kernel(void);
 long long puff_advantage_sm100_launch_count(void);
 /* Synchronises the current device and returns (then clears) the device-side
  * status word: 0, or PUFF_ERR_DEVICE_WAIT when a bounded wait inside a kernel
- * gave up.  Meant for tests and debugging; the launch path never calls it. */
+ * gave up.  The asynchronous launch path never calls it; callers do, at their
+ * own synchronisation points. */
 int puff_advantage_sm100_device_status(void);
+/* Writes `value` into the current device's status word from the host (a plain
+ * copy, nothing is launched): lets tests of a caller's error handling see
+ * PUFF_ERR_DEVICE_WAIT without making any kernel wait.  Returns 0 or a
+ * cudaError_t. */
+int puff_advantage_sm100_inject_status(int value);
 /* Tuning knobs for tests and sweeps (process-wide; value -1 restores the
  * automatic choice; returns the previous value, or PUFF_ERR_VARIANT for an
  * unknown knob).  The initial values come from the environment variables named

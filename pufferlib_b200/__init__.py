@@ -17,4 +17,5 @@ from .advantage import (  # noqa: F401
     priority_probs,
     priority_weights,
     rollout_write,
+    set_variant,
 )

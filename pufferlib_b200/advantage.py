@@ -22,6 +22,15 @@ def _ops():
     return torch.ops.pufferlib
 
 
+def set_variant(name):
+    """Kernel variant of the advantage ops ("auto", "serial", "scan",
+    "generic"); returns the previous one.  The initial setting is "auto", or
+    the environment variable PUFFER_ADV_VARIANT as it stood at the first op
+    call; the op calls themselves read no environment."""
+    prev = _ops().puff_set_variant(cabi.VARIANTS[name])
+    return next(k for k, v in cabi.VARIANTS.items() if v == prev)
+
+
 def compute_puff_advantage(values, rewards, terminals, ratio, advantages,
                            gamma, gae_lambda, vtrace_rho_clip, vtrace_c_clip):
     """In-place V-trace-clipped GAE; returns `advantages` (pufferl.py:660-680).
@@ -69,15 +78,19 @@ def priority_probs(weights, total):
     return _ops().puff_priority_probs(weights, total)
 
 
-def minibatch_gather(advantages, values, prio_probs, idx, anneal_beta):
+def minibatch_gather(advantages, values, prio_probs, idx, anneal_beta, prio_segments=None):
     """What the trainer computes for the sampled segments `idx` (int64, CUDA)
     right after `torch.multinomial` (pufferl.py:363, 373-375, 408-409), in two
     launches.  Returns (mb_values, mb_returns, mb_advantages, adv, mb_prio):
     values[idx], advantages[idx] + values[idx], advantages[idx], the
     priority-weighted normalised advantages
     mb_prio * (a - a.mean()) / (a.std() + 1e-8), and
-    mb_prio = (segments * prio_probs[idx, None]) ** -anneal_beta."""
-    return _ops().puff_minibatch_gather(advantages, values, prio_probs, idx, anneal_beta)
+    mb_prio = (segments * prio_probs[idx, None]) ** -anneal_beta.
+    `prio_segments` is that `segments` factor when it is not the row count of
+    `advantages`: the global segment count of a sharded buffer whose
+    probabilities were normalised over all shards."""
+    return _ops().puff_minibatch_gather(advantages, values, prio_probs, idx, anneal_beta,
+                                        -1 if prio_segments is None else int(prio_segments))
 
 
 def rollout_write(rewards, terminals, values, step_rewards, step_dones, step_values,

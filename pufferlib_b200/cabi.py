@@ -40,6 +40,7 @@ SIGNATURES = {
     "puff_priorities_sm100_probs": (_I, [_P, _P, _P, _LL, _P]),
     "puff_minibatch_sm100_scratch_bytes": (ctypes.c_size_t, [_LL]),
     "puff_minibatch_sm100_gather": (_I, [_P] * 9 + [_F, _LL, _LL, _LL, _P, ctypes.c_size_t, _P]),
+    "puff_minibatch_sm100_gather_ex": (_I, [_P] * 9 + [_F, _LL, _LL, _LL, _LL, _P, ctypes.c_size_t, _P]),
     "puff_minibatch_sm100_bad_index": (_I, []),
     "puff_rollout_sm100_write": (_I, [_P] * 6 + [_LL] * 5 + [_F, _P]),
     "puff_priorities_sm100_weights_noalloc": (_I, [_P, _P, _P, _F, _LL, _P]),
@@ -47,6 +48,7 @@ SIGNATURES = {
     "puff_advantage_sm100_last_kernel": (_I, []),
     "puff_advantage_sm100_launch_count": (_LL, []),
     "puff_advantage_sm100_device_status": (_I, []),
+    "puff_advantage_sm100_inject_status": (_I, [_I]),
     "puff_advantage_sm100_set_tuning": (_I, [_I, _I]),
     "puff_advantage_sm100_version": (ctypes.c_char_p, []),
 }

@@ -570,18 +570,32 @@ namespace puff {
 void count_launch() { g_launch_count.fetch_add(1, std::memory_order_relaxed); }
 }
 
-extern "C" int puff_advantage_sm100_device_status(void)
+namespace puff {
+// Reads (and, when set, clears) the status word of the current device.  The caller has already
+// synchronised the streams whose kernels it asks about.
+int take_device_status()
 {
-    cudaError_t e = cudaDeviceSynchronize();
-    if (e != cudaSuccess) return static_cast<int>(e);
     int h = 0;
-    e = cudaMemcpyFromSymbol(&h, g_device_status, sizeof(int));
+    cudaError_t e = cudaMemcpyFromSymbol(&h, g_device_status, sizeof(int));
     if (e != cudaSuccess) return static_cast<int>(e);
     if (h != 0) {
         const int zero = 0;
         cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
     }
     return h;
+}
+}  // namespace puff
+
+extern "C" int puff_advantage_sm100_device_status(void)
+{
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return take_device_status();
+}
+
+extern "C" int puff_advantage_sm100_inject_status(int value)
+{
+    return static_cast<int>(cudaMemcpyToSymbol(g_device_status, &value, sizeof(int)));
 }
 
 extern "C" int puff_advantage_sm100_set_tuning(int knob, int value)

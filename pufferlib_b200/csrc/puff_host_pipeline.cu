@@ -19,6 +19,7 @@
 #include "../../include/puff_advantage.h"
 
 namespace puff {
+int take_device_status();   // puff_advantage_sm100.cu
 
 constexpr int kSlots = 3;
 constexpr int kMaxDevices = 64;
@@ -153,6 +154,9 @@ extern "C" int puff_advantage_sm100_host(const float* h_values, const float* h_r
             cudaError_t es = cudaStreamSynchronize(p.stream[i]);
             if (es != cudaSuccess && rc == PUFF_OK) rc = static_cast<int>(es);
         }
+        // every kernel of this call has finished: a bounded wait that gave up inside one of them
+        // left part of the output unwritten, which must not be reported as success
+        if (rc == PUFF_OK) rc = take_device_status();
     }
     cudaSetDevice(prev);
     return rc;

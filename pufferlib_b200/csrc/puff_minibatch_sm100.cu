@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(kMbThreads)
 puff_mb_normalize_kernel(const float* __restrict__ mb_adv_raw, const float* __restrict__ prio_probs,
                          const long long* __restrict__ idx, const double* __restrict__ partial, int n_partial,
                          float* __restrict__ mb_adv_norm, float* __restrict__ mb_prio, float anneal_beta,
-                         long long num_segments, long long horizon, long long mb_segments)
+                         long long num_segments, long long prio_segments, long long horizon, long long mb_segments)
 {
     __shared__ double s_part[2 * kMbThreads / 32];
     __shared__ float s_mean, s_denom;
@@ -140,8 +140,10 @@ puff_mb_normalize_kernel(const float* __restrict__ mb_adv_raw, const float* __re
         const long long src_row = idx[m];
         const bool ok = src_row >= 0 && src_row < num_segments;
         // (segments * p) ** -beta, evaluated in fp32 like the reference
-        const float p = ok ? __ldg(prio_probs + src_row) : 0.0f;
-        const float prio = powf(static_cast<float>(num_segments) * p, -anneal_beta);
+        // prio_segments is the N of pufferl.py:363: the segment count the probabilities were
+        // normalised over, which exceeds num_segments when this GPU holds one shard of them.
+        // A row with a bad index gets weight 0, i.e. a zero row (its raw row is zero as well).
+        const float prio = ok ? powf(static_cast<float>(prio_segments) * __ldg(prio_probs + src_row), -anneal_beta) : 0.0f;
         if (lane == 0) mb_prio[m] = prio;
         const float* a = mb_adv_raw + m * horizon;
         float* o = mb_adv_norm + m * horizon;
@@ -149,11 +151,12 @@ puff_mb_normalize_kernel(const float* __restrict__ mb_adv_raw, const float* __re
             for (long long c = 4 * lane; c < horizon; c += 128) {
                 const float4 a4 = *reinterpret_cast<const float4*>(a + c);
                 *reinterpret_cast<float4*>(o + c) =
-                    make_float4(prio * (a4.x - mean) / denom, prio * (a4.y - mean) / denom,
-                                prio * (a4.z - mean) / denom, prio * (a4.w - mean) / denom);
+                    ok ? make_float4(prio * (a4.x - mean) / denom, prio * (a4.y - mean) / denom,
+                                     prio * (a4.z - mean) / denom, prio * (a4.w - mean) / denom)
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         } else {
-            for (long long c = lane; c < horizon; c += 32) o[c] = prio * (a[c] - mean) / denom;
+            for (long long c = lane; c < horizon; c += 32) o[c] = ok ? prio * (a[c] - mean) / denom : 0.0f;
         }
     }
 }
@@ -182,7 +185,19 @@ extern "C" int puff_minibatch_sm100_gather(const float* advantages, const float*
                                            long long mb_segments, void* scratch, size_t scratch_bytes,
                                            void* cuda_stream)
 {
-    if (num_segments < 0 || horizon < 0 || mb_segments < 0) return PUFF_ERR_SHAPE;
+    return puff_minibatch_sm100_gather_ex(advantages, values, prio_probs, idx, mb_values, mb_returns, mb_adv_raw,
+                                          mb_adv_norm, mb_prio, anneal_beta, num_segments, num_segments, horizon,
+                                          mb_segments, scratch, scratch_bytes, cuda_stream);
+}
+
+extern "C" int puff_minibatch_sm100_gather_ex(const float* advantages, const float* values, const float* prio_probs,
+                                              const long long* idx, float* mb_values, float* mb_returns,
+                                              float* mb_adv_raw, float* mb_adv_norm, float* mb_prio,
+                                              float anneal_beta, long long num_segments, long long prio_segments,
+                                              long long horizon, long long mb_segments, void* scratch,
+                                              size_t scratch_bytes, void* cuda_stream)
+{
+    if (num_segments < 0 || horizon < 0 || mb_segments < 0 || prio_segments < num_segments) return PUFF_ERR_SHAPE;
     if (mb_segments == 0 || horizon == 0) return PUFF_OK;
     if (num_segments == 0) return PUFF_ERR_SHAPE;   // nothing to gather from
     if (advantages == nullptr || values == nullptr || prio_probs == nullptr || idx == nullptr ||
@@ -216,10 +231,10 @@ extern "C" int puff_minibatch_sm100_gather(const float* advantages, const float*
     if (nb > 148 * 8) nb = 148 * 8;
     if (vec)
         puff_mb_normalize_kernel<true><<<static_cast<int>(nb), kMbThreads, 0, st>>>(
-            mb_adv_raw, prio_probs, idx, partial, blocks, mb_adv_norm, mb_prio, anneal_beta, num_segments, horizon, mb_segments);
+            mb_adv_raw, prio_probs, idx, partial, blocks, mb_adv_norm, mb_prio, anneal_beta, num_segments, prio_segments, horizon, mb_segments);
     else
         puff_mb_normalize_kernel<false><<<static_cast<int>(nb), kMbThreads, 0, st>>>(
-            mb_adv_raw, prio_probs, idx, partial, blocks, mb_adv_norm, mb_prio, anneal_beta, num_segments, horizon, mb_segments);
+            mb_adv_raw, prio_probs, idx, partial, blocks, mb_adv_norm, mb_prio, anneal_beta, num_segments, prio_segments, horizon, mb_segments);
     count_launch();
     return static_cast<int>(cudaGetLastError());
 }

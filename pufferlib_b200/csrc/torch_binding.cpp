@@ -20,7 +20,9 @@
 #include <torch/all.h>
 #include <torch/library.h>
 
+#include <atomic>
 #include <cstdlib>
+#include <string>
 #include <optional>
 #include <tuple>
 
@@ -62,15 +64,26 @@ static void check_inputs(std::initializer_list<torch::Tensor> tensors, const tor
     TORCH_CHECK(values.is_cuda(), "All tensors must be on GPU");
 }
 
-static int variant_from_env()
+// Kernel variant of the three advantage ops: PUFF_VARIANT_AUTO unless the environment variable
+// PUFFER_ADV_VARIANT (serial | scan | generic) said otherwise when the first op call was made, or
+// puff_set_variant changed it since.  The op calls themselves read no environment.
+static std::atomic<int>& variant_setting()
 {
-    const char* s = std::getenv("PUFFER_ADV_VARIANT");
-    if (s == nullptr) return PUFF_VARIANT_AUTO;
-    const std::string v(s);
-    if (v == "serial") return PUFF_VARIANT_SERIAL;
-    if (v == "scan") return PUFF_VARIANT_SCAN;
-    if (v == "generic") return PUFF_VARIANT_GENERIC;
-    return PUFF_VARIANT_AUTO;
+    static std::atomic<int> v{[] {
+        const char* s = std::getenv("PUFFER_ADV_VARIANT");
+        const std::string name(s == nullptr ? "" : s);
+        return name == "serial" ? PUFF_VARIANT_SERIAL : name == "scan" ? PUFF_VARIANT_SCAN
+             : name == "generic" ? PUFF_VARIANT_GENERIC : PUFF_VARIANT_AUTO;
+    }()};
+    return v;
+}
+static int variant_from_env() { return variant_setting().load(std::memory_order_relaxed); }
+
+// puff_set_variant(v): v in PUFF_VARIANT_* ; returns the previous setting
+int64_t puff_set_variant(int64_t v)
+{
+    TORCH_CHECK(v >= PUFF_VARIANT_AUTO && v <= PUFF_VARIANT_GENERIC, "unknown kernel variant");
+    return variant_setting().exchange(static_cast<int>(v), std::memory_order_relaxed);
 }
 
 // compute_puff_advantage_cuda of cu:53-82
@@ -189,7 +202,7 @@ torch::Tensor puff_priority_probs_cuda(torch::Tensor weights, torch::Tensor tota
 // pufferl.py:363, 373-375, 408-409 for sampled segment indices.
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor>
 puff_minibatch_gather_cuda(torch::Tensor advantages, torch::Tensor values, torch::Tensor prio_probs,
-                           torch::Tensor idx, double anneal_beta)
+                           torch::Tensor idx, double anneal_beta, int64_t prio_segments)
 {
     TORCH_CHECK(advantages.is_cuda(), "All tensors must be on GPU");
     TORCH_CHECK(advantages.dim() == 2 && values.dim() == 2 && advantages.sizes() == values.sizes(),
@@ -215,13 +228,14 @@ puff_minibatch_gather_cuda(torch::Tensor advantages, torch::Tensor values, torch
         mb_prio = torch::empty({M, 1}, opts);
         const size_t sbytes = puff_minibatch_sm100_scratch_bytes(M);
         auto scratch = torch::empty({static_cast<int64_t>((sbytes + 7) / 8)}, opts.dtype(torch::kFloat64));
-        rc = puff_minibatch_sm100_gather(advantages.data_ptr<float>(), values.data_ptr<float>(),
+        // prio_segments < 0: the probabilities were normalised over this tensor's own rows
+        rc = puff_minibatch_sm100_gather_ex(advantages.data_ptr<float>(), values.data_ptr<float>(),
                                          prio_probs.data_ptr<float>(),
                                          reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()),
                                          mb_values.data_ptr<float>(), mb_returns.data_ptr<float>(),
                                          mb_raw.data_ptr<float>(), mb_norm.data_ptr<float>(), mb_prio.data_ptr<float>(),
-                                         static_cast<float>(anneal_beta), S, H, M, scratch.data_ptr<double>(), sbytes,
-                                         at::cuda::getCurrentCUDAStream().stream());
+                                         static_cast<float>(anneal_beta), S, prio_segments < 0 ? S : prio_segments, H, M,
+                                         scratch.data_ptr<double>(), sbytes, at::cuda::getCurrentCUDAStream().stream());
     }
     check_rc(rc, "puff_minibatch_gather");
     return {mb_values, mb_returns, mb_raw, mb_norm, mb_prio};
@@ -274,7 +288,7 @@ std::tuple<torch::Tensor, torch::Tensor> puff_priority_weights_meta(torch::Tenso
 }
 torch::Tensor puff_priority_probs_meta(torch::Tensor weights, torch::Tensor) { return torch::empty_like(weights); }
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor>
-puff_minibatch_gather_meta(torch::Tensor advantages, torch::Tensor, torch::Tensor, torch::Tensor idx, double)
+puff_minibatch_gather_meta(torch::Tensor advantages, torch::Tensor, torch::Tensor, torch::Tensor idx, double, int64_t)
 {
     const int64_t M = idx.size(0), H = advantages.size(1);
     const auto o = advantages.options();
@@ -288,10 +302,11 @@ TORCH_LIBRARY(pufferlib, m)
     m.def("compute_puff_advantage(Tensor(a!) values, Tensor(b!) rewards, Tensor(c!) dones, Tensor(d!) importance, Tensor(e!) advantages, float gamma, float lambda, float rho_clip, float c_clip) -> ()");
     m.def("compute_puff_advantage_prio(Tensor values, Tensor rewards, Tensor dones, Tensor importance, Tensor(a!) advantages, Tensor(b!) seg_abs_sum, float gamma, float lambda, float rho_clip, float c_clip) -> ()");
     m.def("compute_puff_advantage_fill(Tensor values, Tensor rewards, Tensor dones, Tensor importance, Tensor(a!) advantages, Tensor(b!)? seg_abs_sum, float gamma, float lambda, float rho_clip, float c_clip) -> ()");
+    m.def("puff_set_variant(int variant) -> int", &puff_set_variant);
     m.def("puff_priority_weights(Tensor seg_abs_sum, float alpha) -> (Tensor, Tensor)");
     m.def("puff_priority_probs(Tensor weights, Tensor total_w) -> Tensor");
     m.def("puff_rollout_write(Tensor(a!) rewards, Tensor(b!) terminals, Tensor(c!) values, Tensor step_rewards, Tensor step_dones, Tensor step_values, int row_begin, int column, float reward_clip) -> ()");
-    m.def("puff_minibatch_gather(Tensor advantages, Tensor values, Tensor prio_probs, Tensor idx, float anneal_beta) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
+    m.def("puff_minibatch_gather(Tensor advantages, Tensor values, Tensor prio_probs, Tensor idx, float anneal_beta, int prio_segments=-1) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(pufferlib, CUDA, m)

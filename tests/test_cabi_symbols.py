@@ -46,6 +46,16 @@ def test_error_strings_and_validation_without_gpu():
     assert lib.puff_priorities_sm100_weights(z, z, z, 0.5, 5, z, 0, z) == cabi.ERR_NULL
 
 
+def test_device_wait_code_becomes_an_exception():
+    """The code a launch path returns for a given-up in-kernel wait is a
+    RuntimeError on the Python side, like every other failure."""
+    from pufferlib_b200 import cabi
+    assert "bounded wait" in cabi.strerror(cabi.ERR_DEVICE_WAIT)
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        cabi.check(cabi.ERR_DEVICE_WAIT, "puff_advantage_sm100_host")
+    cabi.check(cabi.OK)
+
+
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
 def test_no_cpu_fallback():
     """Without a GPU the product refuses to compute instead of falling back."""

@@ -131,6 +131,27 @@ def test_host_entry_point(name):
     np.testing.assert_allclose(abs_sum.numpy(), exact, rtol=1e-5, atol=1e-6)
 
 
+def test_host_entry_point_reports_a_given_up_wait():
+    """A bounded wait that gave up inside a kernel leaves the output
+    incomplete; the synchronous host entry point must return
+    PUFF_ERR_DEVICE_WAIT for it, not success.  The status word is set from the
+    host here (no kernel is made to wait)."""
+    import pufferlib_b200
+    from pufferlib_b200 import cabi
+    lib = cabi.load()
+    wl = WORKLOADS["cfg0"]
+    host = make_inputs(wl)
+    adv = torch.zeros_like(host[0])
+    assert cabi.device_status() == 0
+    assert lib.puff_advantage_sm100_inject_status(cabi.ERR_DEVICE_WAIT) == 0
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        pufferlib_b200.compute_puff_advantage_host(*host, adv, *wl.hyper())
+    assert cabi.device_status() == 0                       # reported once, then cleared
+    pufferlib_b200.compute_puff_advantage_host(*host, adv, *wl.hyper())   # and the next call is clean
+    want = oracle_advantage([t.numpy() for t in host], wl.hyper(), sentinel=0.0)
+    assert bits_equal(adv.numpy(), want)
+
+
 def test_host_entry_point_many_blocks(monkeypatch):
     """Small row blocks so that the slot ring wraps many times; pageable memory."""
     import pufferlib_b200
@@ -237,6 +258,31 @@ def test_minibatch_gather_flags_bad_indices():
     assert cabi.load().puff_minibatch_sm100_bad_index() == 1
     assert cabi.load().puff_minibatch_sm100_bad_index() == 0      # cleared by the read
     assert torch.equal(mv[:2], val[idx[:2]]) and torch.all(mv[2:] == 0)
+    # a bad index is a zero row with zero weight in every output, never inf or NaN
+    assert torch.all(mr[2:] == 0) and torch.all(ma[2:] == 0) and torch.all(an[2:] == 0) and torch.all(mp[2:] == 0)
+    assert torch.isfinite(an).all() and torch.isfinite(mp).all()
+
+
+def test_minibatch_gather_of_a_shard_uses_the_global_segment_count():
+    """Rows sharded over ranks, probabilities normalised over all of them: the
+    N of (N * p) ** -beta (pufferl.py:363) is the global count, passed apart
+    from the local row count that bounds the indices."""
+    import pufferlib_b200
+    g = torch.Generator().manual_seed(11)
+    S_global, S_local, H, M, beta = 4096, 1024, 64, 128, 0.6
+    adv = torch.randn(S_local, H, generator=g).cuda()
+    val = torch.randn(S_local, H, generator=g).cuda()
+    probs = (torch.rand(S_local, generator=g) + 0.01).cuda()
+    probs = probs / probs.sum() * (S_local / S_global)       # this shard's slice of a global distribution
+    idx = torch.randint(0, S_local, (M,), generator=g).cuda()
+    *_, an, mp = pufferlib_b200.minibatch_gather(adv, val, probs, idx, beta, prio_segments=S_global)
+    e_prio = (S_global * probs[idx, None]) ** -beta
+    np.testing.assert_allclose(mp.cpu().numpy(), e_prio.cpu().numpy(), rtol=1e-5)
+    e = adv[idx]
+    e = e_prio * (e - e.mean()) / (e.std() + 1e-8)
+    np.testing.assert_allclose(an.cpu().numpy(), e.cpu().numpy(), rtol=1e-4, atol=1e-5)
+    with pytest.raises(RuntimeError):
+        pufferlib_b200.minibatch_gather(adv, val, probs, idx, beta, prio_segments=S_local - 1)
 
 
 def test_rollout_write_matches_the_trainer_assignments():
