@@ -27,11 +27,17 @@ _f32p = ctypes.POINTER(ctypes.c_float)
 _f64p = ctypes.POINTER(ctypes.c_double)
 
 
+def reference_root():
+    """Where the reference checkout is looked for: $PUFFER_REFERENCE_ROOT, else
+    a folder `reference` beside this repository.  It need not exist."""
+    return os.environ.get("PUFFER_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
 def build(ref=True, ref_cuda=False):
     """Compile the oracle (and, when the reference tree is mounted, the
     reference build under oracle/_ref/).  Existing outputs are kept."""
     targets = ["oracle"]
-    ref_root = os.environ.get("PUFFER_REFERENCE_ROOT", "/root/reference")
+    ref_root = reference_root()
     have_ref = os.path.isfile(os.path.join(ref_root, "pufferlib", "extensions", "pufferlib.cpp"))
     if ref and have_ref:
         targets.append("ref")

@@ -32,6 +32,12 @@ TORCH_EXT = os.path.join(HERE, "_C.so")
 CU_SOURCES = ["puff_advantage_sm100.cu", "puff_priorities_sm100.cu", "puff_minibatch_sm100.cu",
               "puff_rollout_sm100.cu", "puff_host_pipeline.cu"]
 
+# --fmad=true leaves nvcc free to contract a*b+c into an FMA.  One such contraction in the
+# recurrence changes the last bit of about half of the outputs, so every kernel that must be
+# bit-exact (tma2d, bulk1d, generic, and the replay step of scan) spells its arithmetic with
+# __fmul_rn / __fadd_rn / __fsub_rn and their f32x2 forms, which are never contracted.  Only code
+# that is checked against a tolerance (the scan kernel's carry composition, the minibatch
+# normalisation, the priority weights) is written with plain operators and may be fused.
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--ftz=false", "--prec-div=true", "--prec-sqrt=true", "--fmad=true",

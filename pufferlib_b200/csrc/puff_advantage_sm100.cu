@@ -35,6 +35,7 @@
 // PUFF_ERR_DEVICE_WAIT in a status word, drains its own stores and returns.
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 #include <stdint.h>
 #include <stdlib.h>
 
@@ -322,12 +323,23 @@ extern "C" int puff_advantage_sm100_launch(const float* values, const float* rew
                                           rho_clip, c_clip, num_segments, horizon, variant, 0u, cuda_stream);
 }
 
+namespace puff {
+// NVTX range "puff_advantage" around the host side of every launch, so that a timeline shows the
+// op by name (the reference trainer books it under its "train_misc" section, pufferl.py:349).
+// Header-only NVTX: a no-op costing a few nanoseconds unless a profiler has injected itself.
+struct LaunchRange {
+    LaunchRange() { nvtxRangePushA("puff_advantage"); }
+    ~LaunchRange() { nvtxRangePop(); }
+};
+}  // namespace puff
+
 extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* rewards, const float* dones,
                                               const float* importance, float* advantages, float* seg_abs_sum,
                                               float gamma, float lambda, float rho_clip, float c_clip,
                                               long long num_segments, long long horizon, int variant,
                                               unsigned flags, void* cuda_stream)
 {
+    const LaunchRange nvtx_range;
     t_last_kernel = PUFF_KERNEL_NONE;
     if (num_segments < 0 || horizon < 0) return PUFF_ERR_SHAPE;
     if (variant < PUFF_VARIANT_AUTO || variant > PUFF_VARIANT_GENERIC) return PUFF_ERR_VARIANT;
