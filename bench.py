@@ -5,19 +5,26 @@
 
 A step is one pass of the path over one `[segments, horizon]` fp32 buffer that
 is already resident in HBM: the advantage kernel with its fused per-segment
-|advantage| sums, the priority weights, (N > 1) the all-reduce of the weight
-total, and the sampling probabilities.  The three small launches and the
-all-reduce of step i run on a side stream while the advantage kernel of step
-i+1 runs; all K steps finish inside the timed region.  With N GPUs every rank owns its own
-shard of `segments` rows (weak scaling: the global buffer has N x segments
-rows), exactly one process per GPU.
+|advantage| sums, the priority weights, (N > 1) the exchange of the weight
+total between the GPUs, and the sampling probabilities.  The small launches of
+step i run on a side stream while the advantage kernel of step i+1 runs; all K
+steps finish inside the timed region.
+
+With N GPUs (one process per GPU) the headline is weak scaling: every rank owns
+its own `segments x horizon` buffer.  Every N > 1 line also carries
+`strong_scaling`: ONE buffer of that size split by rows over the ranks, with
+the kernel-only and the kernel + exchange times of a step.  The weight total
+crosses GPUs inside the priority kernels (stores into peer-mapped mailboxes);
+`--exchange nccl` uses a torch.distributed all-reduce instead.
 
 One JSON line is printed by rank 0.  `value` is the whole-job rate with
 device-resident inputs, `e2e` the same metric through the host-buffer C-ABI
 entry point with pinned host inputs and outputs (copies inside the timed
-region), `roofline` the advantage kernel's algorithmic bytes over its
-CUDA-event duration against the measured HBM copy peak, and `cpu_baseline` the
-reference CPU op timed on this machine's cores.
+region) beside the time of its bare copies, `roofline` the advantage kernel's
+algorithmic bytes over its CUDA-event duration against the measured HBM copy
+peak, `small_workloads` (N = 1) the steady-state kernel time of the other
+configurations with a parity bit each, and `cpu_baseline` the reference CPU op
+timed on this machine's cores.
 
 `--impl reference` times only the reference's own CPU implementation (the
 build under oracle/_ref/ when present, else the oracle port) and prints the
@@ -226,7 +233,7 @@ def run_reference_arm(args, wl, rank, world):
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": 1e3 * dt / steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": workload_config(wl, args.gpus, "reference CPU op"),
+        "config": workload_config(wl, args.gpus),
         "cpu_baseline": {"value": value, "unit": "elements/s", "cores": cores, "kind": kind,
                          "sample": f"each step: one pass over the first {rows} of {wl.segments} segments x {wl.horizon}, "
                                    f"row slices on {cores} threads (the op itself is single-threaded)",
@@ -237,192 +244,298 @@ def run_reference_arm(args, wl, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(wl, n_gpus, what):
-    return {"workload": f"{wl.name}: {wl.segments}x{wl.horizon} fp32 per GPU ({what})",
+def workload_config(wl, n_gpus):
+    """The `config` object, identical in the B200 arm and the reference arm."""
+    set_bytes = BYTES_PER_ELEMENT * wl.elements
+    n_sets = rotation_sets(set_bytes)
+    return {"workload": f"{wl.name}: {wl.segments}x{wl.horizon} fp32 per GPU",
             "segments_per_gpu": wl.segments, "horizon": wl.horizon,
             "global_segments": wl.segments * n_gpus,
             "gamma": wl.gamma, "lambda": wl.lam, "rho_clip": wl.rho_clip, "c_clip": wl.c_clip,
-            "parallelism": f"segments sharded over {n_gpus} GPU(s), one scalar all-reduce per step"
-                           if n_gpus > 1 else "single GPU"}
+            "parallelism": f"segments sharded over {n_gpus} GPU(s), one fp64 scalar exchanged per step"
+                           if n_gpus > 1 else "single GPU",
+            "l2": "inputs larger than L2" if n_sets == 1 else
+                  f"rotating over {n_sets} buffer sets ({n_sets * set_bytes >> 20} MiB > 2x L2)"}
+
+
+def rotation_sets(set_bytes):
+    """Buffer sets to rotate over so that consecutive launches never find their inputs in L2."""
+    return 1 if set_bytes >= 2 * L2_BYTES else -(-2 * L2_BYTES // set_bytes)
 
 
 # ---------------------------------------------------------------------------
 # the B200 arm
 # ---------------------------------------------------------------------------
+MAX_GRAPH_STEPS = 500
+
+
+class PathTimer:
+    """Times the hot path over one rank's buffers.
+
+    step(i): advantage kernel (+ fused sums) on the current stream; priority
+    weights, the cross-GPU exchange of their total and the probabilities behind
+    it on a side stream, overlapping the advantage kernel of step i+1.  The
+    loops are captured into CUDA graphs (all steps in one graph, up to
+    MAX_GRAPH_STEPS per graph) and replayed: the per-step host work -- operator
+    calls on every rank -- is otherwise comparable to the kernel time.  The
+    side stream joins the main one once per graph, inside the timed region."""
+
+    def __init__(self, wl_local, host_inputs, dev, sharded, hyper, world, fence):
+        self.S, self.H = wl_local.segments, wl_local.horizon
+        self.elems = self.S * self.H
+        self.hyper, self.sharded, self.world, self.fence = hyper, sharded, world, fence
+        self.n_sets = rotation_sets(BYTES_PER_ELEMENT * self.elems)
+        self.sets = []
+        for i in range(self.n_sets):
+            ins = [t.to(dev) for t in host_inputs] if i == 0 else [t.clone() for t in self.sets[0][:4]]
+            # DEPTH sum buffers per set: the priority launches of step i read one on the side
+            # stream while the advantage kernels of the following steps fill the others
+            self.sets.append(ins + [torch.zeros((self.S, self.H), device=dev),
+                                    tuple(torch.empty(self.S, device=dev) for _ in range(DEPTH))])
+        self.side_stream = torch.cuda.Stream(priority=-1)
+        self.capture_stream = torch.cuda.Stream()
+        self.pending = collections.deque()
+        self.last = {}
+        self.windows = []
+
+    # -- one step in its three forms -------------------------------------------
+    def step(self, i):
+        v, r, d, w, adv, abs2 = self.sets[i % self.n_sets]
+        main = torch.cuda.current_stream()
+        while len(self.pending) >= DEPTH:      # the sum buffer of step i-DEPTH is free again
+            main.wait_event(self.pending.popleft())
+        probs, total, done = self.sharded.step_overlapped(v, r, d, w, adv, abs2[i % DEPTH], self.side_stream)
+        self.pending.append(done)
+        self.last["probs"], self.last["total"] = probs, total
+
+    def step_serial(self, i):
+        """Everything on one stream: kernel, then weights, exchange, probabilities."""
+        v, r, d, w, adv, abs2 = self.sets[i % self.n_sets]
+        self.sharded.kernels.advantage_prio(v, r, d, w, adv, abs2[i % DEPTH], self.hyper)
+        self.last["probs"], self.last["total"] = self.sharded.priorities(abs2[i % DEPTH])
+
+    def adv_only(self, i):
+        v, r, d, w, adv, abs2 = self.sets[i % self.n_sets]
+        self.sharded.kernels.advantage_prio(v, r, d, w, adv, abs2[i % DEPTH], self.hyper)
+
+    def drain(self):
+        main = torch.cuda.current_stream()
+        while self.pending:
+            main.wait_event(self.pending.popleft())
+
+    # -- timing -----------------------------------------------------------------
+    def _capture(self, fn, count):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=self.capture_stream):
+            for i in range(count):
+                fn(i)
+            self.drain()          # join the side stream back into the capture
+        return g
+
+    def warm(self, fn, count):
+        with torch.cuda.stream(self.capture_stream):
+            for i in range(count):
+                fn(i)
+            self.drain()
+        self.fence()
+
+    def timed_graph(self, fn, total_steps):
+        """ms for `total_steps` steps of fn, replayed from graphs; every launch of every step
+        (side stream included) ends inside the timed region."""
+        from pufferlib_b200 import cabi
+        per = max(min(total_steps, MAX_GRAPH_STEPS), min(self.n_sets, total_steps))
+        full, rem = divmod(total_steps, per)
+        g_full = self._capture(fn, per)
+        g_rem = self._capture(fn, rem) if rem else None
+        g_full.replay()
+        self.fence()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.time()
+        t0.record()
+        for _ in range(full):
+            g_full.replay()
+        if g_rem is not None:
+            g_rem.replay()
+        t1.record()
+        self.fence()
+        self.windows.append((w0, time.time()))
+        status = cabi.device_status()
+        if status != 0:
+            raise SystemExit(f"bench.py: a kernel reported status {status} ({cabi.strerror(status)}) in the timed region")
+        return t0.elapsed_time(t1), per
+
+    def timed_eager(self, fn, total_steps):
+        from pufferlib_b200 import cabi
+        self.fence()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.time()
+        t0.record()
+        for i in range(total_steps):
+            fn(i)
+        self.drain()                 # every step's side-stream work ends inside the timed region
+        t1.record()
+        self.fence()
+        self.windows.append((w0, time.time()))
+        status = cabi.device_status()
+        if status != 0:
+            raise SystemExit(f"bench.py: a kernel reported status {status} ({cabi.strerror(status)}) in the timed region")
+        return t0.elapsed_time(t1), 1
+
+
+def max_over_ranks(values, dev, world):
+    if world == 1:
+        return [float(v) for v in values]
+    import torch.distributed as dist
+    t = torch.tensor(list(values), device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) for x in t]
+
+
+def numa_bind(local_rank):
+    """Run this process (and so place its pinned buffers, first touch) on the CPUs of the NUMA
+    node its GPU hangs off, when the machine says which that is.  Returns what was done."""
+    try:
+        props = torch.cuda.get_device_properties(local_rank)
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return {"node": None, "why": "the GPU reports no NUMA node"}
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return {"node": node, "why": "none of the node's CPUs is in this process's affinity mask"}
+        os.sched_setaffinity(0, cpus)
+        return {"node": node, "cpus": len(cpus)}
+    except Exception as exc:
+        return {"node": None, "why": str(exc)[:120]}
+
+
 def run_b200_arm(args, wl, rank, local_rank, world):
     import torch.distributed as dist
     import pufferlib_b200
     from pufferlib_b200 import cabi
     from pufferlib_b200.sharded import ShardedAdvantage
+    from pufferlib_b200.workloads import shard_rows
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the B200 arm has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa = numa_bind(local_rank) if world > 1 else None    # before any pinned allocation
+    exchange, exchange_kind = None, "none (single GPU)"
     if world > 1:
-        # the tiny all-reduce has to slip in between persistent advantage kernels that
-        # fill every SM: give NCCL's stream (and the side stream below) high priority
+        # the collective fallback's kernel has to slip in beside persistent advantage kernels
+        # that fill every SM: give NCCL's stream (and the side stream) high priority
         opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
         dist.init_process_group("nccl", device_id=dev, pg_options=opts)
-
-    S, H = wl.segments, wl.horizon
-    hyper = wl.hyper()
-    elems = S * H
-    set_bytes = BYTES_PER_ELEMENT * elems
-    # inputs larger than L2: either one buffer set already is, or rotate over enough sets
-    n_sets = 1 if set_bytes >= 2 * L2_BYTES else -(-2 * L2_BYTES // set_bytes)
-    host = make_inputs(wl.with_segments(S, seed=wl.seed + rank), pin=True)
-    sets = []
-    for i in range(n_sets):
-        ins = [t.to(dev) for t in host] if i == 0 else [t.clone() for t in sets[0][:4]]
-        # DEPTH sum buffers per set: the priority launches of step i read one on the side
-        # stream while the advantage kernels of the following steps fill the others
-        sets.append(ins + [torch.zeros((S, H), device=dev), tuple(torch.empty(S, device=dev) for _ in range(DEPTH))])
-    sharded = ShardedAdvantage(S * world, H, hyper, PRIO_ALPHA, rank=rank, world=world)
-    variant = args.variant
-    pufferlib_b200.set_variant(variant)
-    side_stream = torch.cuda.Stream(priority=-1)
-    pending = collections.deque()
-    last = {}
-
-    def step(i, ev=None):
-        """One pass: advantage kernel (+ fused sums) on the current stream, priority
-        weights / all-reduce / probabilities behind it on the side stream."""
-        v, r, d, w, adv, abs2 = sets[i % n_sets]
-        main = torch.cuda.current_stream()
-        while len(pending) >= DEPTH:      # the sum buffer of step i-DEPTH is free again
-            main.wait_event(pending.popleft())
-        if ev is not None:
-            ev[0].record()
-        if args.no_overlap:
-            sharded.kernels.advantage_prio(v, r, d, w, adv, abs2[i % DEPTH], hyper)
-            if ev is not None:
-                ev[1].record()
-            last["probs"], last["total"] = sharded.priorities(abs2[i % DEPTH])
-            return
-        probs, total, done = sharded.step_overlapped(v, r, d, w, adv, abs2[i % DEPTH], side_stream)
-        if ev is not None:
-            ev[1].record()      # recorded on the main stream: brackets the advantage kernel only
-        pending.append(done)
-        last["probs"], last["total"] = probs, total
-
-    def drain():
-        main = torch.cuda.current_stream()
-        while pending:
-            main.wait_event(pending.popleft())
+        exchange_kind = "torch.distributed all-reduce (NCCL)"
+        if args.exchange == "p2p":
+            try:
+                from pufferlib_b200.exchange import PeerExchange
+                exchange = PeerExchange.for_process_group()
+                exchange_kind = "peer stores inside the priority kernels (puff_exchange, CUDA IPC mailboxes)"
+            except Exception as exc:
+                exchange_kind += f"; peer exchange unavailable: {str(exc)[:120]}"
+            # all ranks must agree, or half of them would wait for pushes that never come
+            ok = torch.tensor([1 if exchange is not None else 0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok) == 0 and exchange is not None:
+                exchange.close()
+                exchange = None
+                exchange_kind = "torch.distributed all-reduce (NCCL); peer exchange unavailable on another rank"
+    if args.reserve_sms > 0:
+        cabi.set_tuning(reserve_sms=args.reserve_sms)
 
     def fence():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    S, H = wl.segments, wl.horizon
+    hyper = wl.hyper()
+    elems = S * H
+    variant = args.variant
+    pufferlib_b200.set_variant(variant)
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
-    for i in range(warmup):
-        step(i)
-    drain()
+
+    # ---- headline: every rank owns its own S x H buffer (weak scaling) ------------
+    host = make_inputs(wl.with_segments(S, seed=wl.seed + rank), pin=True)
+    sharded = ShardedAdvantage(S * world, H, hyper, PRIO_ALPHA, rank=rank, world=world, exchange=exchange)
+    timer = PathTimer(wl, host, dev, sharded, hyper, world, fence)
+    timer.warm(timer.step, max(warmup, timer.n_sets))
     kernel_name = cabi.last_kernel()
-    fence()
-
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    windows = []
-    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    def adv_only(i):
-        v, r, d, w, adv, abs2 = sets[i % n_sets]
-        sharded.kernels.advantage_prio(v, r, d, w, adv, abs2[i % DEPTH], hyper)
-
-    # The timed loop is captured into CUDA graphs and replayed: a buffer set that fits
-    # L2 many times over makes a step of a few microseconds, and with N > 1 the per-step
-    # host work (operator calls plus a torch.distributed all-reduce on every rank) comes
-    # close to the kernel time, so eager launches would measure Python.  NCCL collectives
-    # are capturable.  --no-graph times eager launches instead.
-    use_graph = not args.no_graph
-    graph_steps = n_sets if n_sets > 1 else 10
-    if use_graph:
-        side = torch.cuda.Stream()
-
-        def capture(fn, count):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                for i in range(count):
-                    fn(i)
-                drain()          # join the side stream back into the capture
-            return g
-
-        def timed_replays(fn, total_steps):
-            per = min(total_steps, graph_steps)
-            full, rem = divmod(total_steps, per)
-            g_full = capture(fn, per)
-            g_rem = capture(fn, rem) if rem else None
-            g_full.replay()
-            fence()
-            l0 = cabi.launch_count()
-            w0 = time.time()
-            t_start.record()
-            for _ in range(full):
-                g_full.replay()
-            if g_rem is not None:
-                g_rem.replay()
-            t_stop.record()
-            fence()
-            windows.append((w0, time.time()))
-            return t_start.elapsed_time(t_stop), cabi.launch_count() - l0
-
-        with torch.cuda.stream(side):
-            for i in range(n_sets):
-                step(i)
-            drain()
-        fence()
-        lc0 = cabi.launch_count()
-        step(0)
-        drain()
-        launches_per_step = cabi.launch_count() - lc0
-        ms_total, _ = timed_replays(step, steps)
-        launches = launches_per_step * steps      # replays re-run the captured launches
-        ko_total, _ = timed_replays(adv_only, steps)
-        ko_ms = ko_total / steps
-        kernel_ms = ko_ms   # back-to-back launches of the advantage kernel alone, launch gaps included
-        timing = (f"CUDA graphs of {min(steps, graph_steps)} steps replayed; "
-                  "kernel time = graph of advantage launches only (launch gaps included)")
-    else:
-        # ---- device-resident timing, eager -----------------------------------
-        kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-        launches0 = cabi.launch_count()
-        fence()
-        w0 = time.time()
-        t_start.record()
-        for i in range(steps):
-            step(i, kev[i])
-        drain()                 # every step's side-stream work ends inside the timed region
-        t_stop.record()
-        fence()
-        windows.append((w0, time.time()))
-        launches = cabi.launch_count() - launches0
-        ms_total = t_start.elapsed_time(t_stop)
-        kernel_ms = sum(a.elapsed_time(b) for a, b in kev) / steps
-        # ---- kernel-only loop (no events between launches, no priorities) ----
-        fence()
-        t_start.record()
-        for i in range(steps):
-            adv_only(i)
-        t_stop.record()
-        fence()
-        ko_ms = t_start.elapsed_time(t_stop) / steps
-        timing = "eager launches; kernel time = CUDA events around every advantage launch in the timed loop"
-    if world > 1:
-        t = torch.tensor([ms_total, kernel_ms, ko_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, kernel_ms, ko_ms = float(t[0]), float(t[1]), float(t[2])
+    lc0 = cabi.launch_count()
+    timer.step(0)
+    timer.drain()
+    launches_per_step = cabi.launch_count() - lc0
+    fence()
+    timed = timer.timed_eager if args.no_graph else timer.timed_graph
+    ms_total, per_graph = timed(timer.step, steps)
+    ko_total, _ = timed(timer.adv_only, steps)
+    launches = launches_per_step * steps          # graph replays re-run the captured launches
+    ms_total, ko_total = max_over_ranks([ms_total, ko_total], dev, world)
+    kernel_ms = ko_total / steps                   # back-to-back advantage launches alone, launch gaps included
     value = elems * world * steps / (ms_total * 1e-3)
+    timing = ("eager launches" if args.no_graph else
+              f"CUDA graphs of {per_graph} steps replayed, side stream joined once per graph") + \
+             "; kernel time = the same loop with the advantage launches only (launch gaps included)"
+
+    # ---- the contract's split: ONE S x H buffer sharded over the ranks (strong scaling) ----
+    strong = None
+    if world > 1 and not args.no_strong:
+        lo, hi = shard_rows(S, rank, world)
+        full = make_inputs(wl)                     # the same global buffer on every rank
+        local = [t[lo:hi].contiguous() for t in full]
+        del full
+        wl_local = wl.with_segments(hi - lo)
+        sh = ShardedAdvantage(S, H, hyper, PRIO_ALPHA, rank=rank, world=world, exchange=exchange)
+        st = PathTimer(wl_local, local, dev, sh, hyper, world, fence)
+        st.warm(st.step, max(warmup, st.n_sets))
+        n = max(steps, 200)                        # short steps: time enough of them
+        a, _ = st.timed_graph(st.step, n)
+        b, _ = st.timed_graph(st.adv_only, n)
+        c, _ = st.timed_graph(st.step_serial, n)
+        a, b, c = max_over_ranks([a, b, c], dev, world)
+        strong = {"scaling": "strong", "global_segments": S, "segments_per_gpu": hi - lo, "steps": n,
+                  "value": elems * n / (a * 1e-3), "unit": "elements/s", "ms_per_step": a / n,
+                  "kernel_only_us": 1e3 * b / n, "kernel_plus_exchange_serial_us": 1e3 * c / n,
+                  "exchange_serial_us": 1e3 * (c - b) / n,
+                  "l2": f"rotating over {st.n_sets} buffer sets" if st.n_sets > 1 else "inputs larger than L2",
+                  "what": "ms_per_step: exchange overlapped with the next step's kernel (as the headline); "
+                          "kernel_plus_exchange_serial_us: kernel, weights, exchange, probabilities on one stream"}
+        timer.windows += st.windows
+        del st, local
+
+    # ---- small and odd workloads: steady-state kernel time (single GPU only) -------
+    small = None
+    if world == 1 and not args.no_small and args.workload == "cfg2" and args.segments == 0:
+        small = time_small_workloads(dev, fence)
 
     # ---- the reference's own CUDA kernel on this GPU (secondary baseline) -----
     ref_cuda = None
     if rank == 0 and not args.no_ref_cuda:
-        ref_cuda = time_reference_cuda_kernel(sets, n_sets, hyper, elems)
+        ref_cuda = time_reference_cuda_kernel(timer.sets, timer.n_sets, hyper, elems)
 
     # ---- the 9-argument torch op, eager, launch cost included ----------------
-    op_call = time_torch_op(sets, n_sets, hyper, elems) if rank == 0 else None
+    op_call = time_torch_op(timer.sets, timer.n_sets, hyper, elems) if rank == 0 else None
+
+    # ---- CPU baseline (and the parity bits of the small workloads: the oracle as checker) ----
+    cpu_line = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_reference_rate(wl, seconds_budget=6.0)
+        cpu_line = {"value": cpu["pooled"], "unit": "elements/s", "cores": cpu["cores"],
+                    "kind": cpu["kind"], "sample": cpu["sample"], "single_thread_value": cpu["single"]}
+        if small is not None:
+            check_small_workloads(small)
+    if small is not None:
+        for row in small:
+            row.pop("_got", None)
 
     # ---- end to end through the host-buffer C ABI ----------------------------
     e2e = None
@@ -430,66 +543,185 @@ def run_b200_arm(args, wl, rank, local_rank, world):
         e2e_steps = max(2, min(steps, args.e2e_steps))
         h_adv = torch.zeros((S, H)).pin_memory()
         h_abs = torch.zeros(S).pin_memory()
-        for _ in range(2):
+        lib = cabi.load()
+
+        def host_call():
             pufferlib_b200.compute_puff_advantage_host(*host, h_adv, *hyper, seg_abs_sum=h_abs,
                                                        variant=variant, device=local_rank)
-        fence()
-        w0 = time.time()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            pufferlib_b200.compute_puff_advantage_host(*host, h_adv, *hyper, seg_abs_sum=h_abs,
-                                                       variant=variant, device=local_rank)
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
-        fence()
-        windows.append((w0, time.time()))
-        if world > 1:
-            t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_s = float(t[0])
+
+        def copies_only():
+            cabi.check(lib.puff_advantage_sm100_host_copies_only(*[t.data_ptr() for t in host], h_adv.data_ptr(),
+                                                                 h_abs.data_ptr(), S, H, local_rank))
+
+        def wall(fn, n):
+            for _ in range(2):
+                fn()
+            fence()
+            w0 = time.time()
+            t0 = time.perf_counter()
+            for _ in range(n):
+                fn()
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            fence()
+            timer.windows.append((w0, time.time()))
+            return max_over_ranks([dt], dev, world)[0]
+
+        ceil_s = wall(copies_only, e2e_steps)      # first: it leaves garbage in h_adv, the real run overwrites it
+        e2e_s = wall(host_call, e2e_steps)
         e2e = {"value": elems * world * e2e_steps / e2e_s, "unit": "elements/s",
                "h2d_bytes_per_step": 16 * elems * world,
                "d2h_bytes_per_step": (4 * S * (H - 1) + 4 * S) * world, "steps": e2e_steps,
                "ms_per_step": 1e3 * e2e_s / e2e_steps,
+               "copy_ceiling_ms": 1e3 * ceil_s / e2e_steps,
+               "frac_of_copy_ceiling": ceil_s / e2e_s,
+               "copy_ceiling": "the same blocks, streams and bytes with no kernel between the copies "
+                               "(puff_advantage_sm100_host_copies_only), all ranks at once",
+               "numa": numa,
                "api": "puff_advantage_sm100_host (C ABI, pinned host buffers)"}
 
-    clocks = sampler.stop(windows) if sampler is not None else None
+    clocks = sampler.stop(timer.windows) if sampler is not None else None
 
     if rank == 0:
         peak, peak_kind = hbm_peak()
         achieved = BYTES_PER_ELEMENT * elems / (kernel_ms * 1e-3) / 1e9
+        traffic = TRAFFIC.get((wl.name, kernel_name)) if wl.segments == WORKLOADS[wl.name].segments else None
         line = {
             "metric": "advantage elements/sec", "value": value, "unit": "elements/s",
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_total / steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": dict(workload_config(wl, world, f"variant {variant}, kernel {kernel_name}"),
-                           l2="inputs larger than L2" if n_sets == 1 else
-                              f"rotating over {n_sets} buffer sets ({n_sets * set_bytes >> 20} MiB > 2x L2)"),
+            "config": workload_config(wl, world),
+            "variant": variant, "kernel": kernel_name, "exchange": exchange_kind,
             "achieved_gbs": value * BYTES_PER_ELEMENT / 1e9,
-            "kernel_only": {"ms_per_launch": ko_ms, "elements_per_s": elems * world / (ko_ms * 1e-3),
-                            "gbs_per_gpu": BYTES_PER_ELEMENT * elems / (ko_ms * 1e-3) / 1e9},
+            "kernel_only": {"ms_per_launch": kernel_ms, "elements_per_s": elems * world / (kernel_ms * 1e-3),
+                            "gbs_per_gpu": BYTES_PER_ELEMENT * elems / (kernel_ms * 1e-3) / 1e9},
             "timing": timing,
             "reference_cuda_kernel": ref_cuda,
-        "torch_op_eager": op_call,
+            "torch_op_eager": op_call,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
-                         "traffic": TRAFFIC.get((wl.name, kernel_name)) if wl.segments == WORKLOADS[wl.name].segments else None,
+                         "traffic": None if traffic is None else traffic["read"] + traffic["write"],
+                         "traffic_read": None if traffic is None else traffic["read"],
+                         "traffic_write": None if traffic is None else traffic["write"],
+                         "traffic_source": None if traffic is None else traffic["source"],
                          "kernel": kernel_name, "kernel_ms": kernel_ms, "peak_kind": f"of {peak_kind}",
                          "algorithmic_bytes": BYTES_PER_ELEMENT * elems},
             "e2e": e2e,
             "gpu_launches": launches,
             "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu:
-            cpu = cpu_reference_rate(wl, seconds_budget=6.0)
-            line["cpu_baseline"] = {"value": cpu["pooled"], "unit": "elements/s", "cores": cpu["cores"],
-                                    "kind": cpu["kind"], "sample": cpu["sample"],
-                                    "single_thread_value": cpu["single"]}
+        if strong is not None:
+            line["strong_scaling"] = strong
+        if small is not None:
+            line["small_workloads"] = small
+        if cpu_line is not None:
+            line["cpu_baseline"] = cpu_line
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
+        if exchange is not None:
+            exchange.close()
         dist.destroy_process_group()
+
+
+# Workloads that are too small (or too odd) for the headline, measured as steady state:
+# back-to-back launches rotating over buffer sets larger than 2x L2.
+def small_workload_list():
+    from pufferlib_b200.workloads import Workload
+    return [WORKLOADS["cfg0"], WORKLOADS["cfg1"], WORKLOADS["cfg3"], WORKLOADS["cfg4"],
+            # the shipped odd horizon: config/ocean/drive.ini:36-39 (745472 // 91 = 8192 segments)
+            Workload("drive", 8192, 91, gamma=0.98, lam=0.95, seed=7, epilogue=True),
+            # an odd horizon at the headline's scale
+            Workload("odd_large", 131072, 127, seed=8, epilogue=True)]
+
+
+def time_small_workloads(dev, fence):
+    from pufferlib_b200 import cabi
+    from pufferlib_b200.advantage import launch_raw
+    peak, _ = hbm_peak()
+    rows = []
+    stream = torch.cuda.Stream()
+    for wl in small_workload_list():
+        S, H = wl.segments, wl.horizon
+        hyper = wl.hyper()
+        set_bytes = BYTES_PER_ELEMENT * S * H
+        n_sets = rotation_sets(set_bytes)
+        host = make_inputs(wl)
+        first = [t.to(dev) for t in host]
+        sets = [first + [torch.zeros((S, H), device=dev), torch.empty(S, device=dev)]]
+        for _ in range(n_sets - 1):
+            sets.append([t.clone() for t in first] + [torch.zeros((S, H), device=dev), torch.empty(S, device=dev)])
+
+        def launch(i):
+            v, r, d, w, adv, sums = sets[i % n_sets]
+            launch_raw(v, r, d, w, adv, *hyper, seg_abs_sum=sums, variant=wl.variant)
+
+        n = max(n_sets, 200)
+        with torch.cuda.stream(stream):
+            for i in range(min(n, 2 * n_sets)):
+                launch(i)
+        kernel = cabi.last_kernel()
+        fence()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(n):
+                launch(i)
+        g.replay()
+        fence()
+        times = []
+        for _ in range(5):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            g.replay()
+            t1.record()
+            torch.cuda.synchronize()
+            times.append(t0.elapsed_time(t1) / n)
+        us = 1e3 * statistics.median(times)
+        gbs = set_bytes / (us * 1e-6) / 1e9
+        rows.append({"workload": f"{wl.name}: {S}x{H}", "kernel": kernel, "variant": wl.variant,
+                     "us_per_launch": us, "gbs": gbs, "frac": gbs / peak,
+                     "traffic_floor_us": 1e6 * set_bytes / (peak * 1e9), "buffer_sets": n_sets,
+                     "_got": (wl, sets[0][4].cpu(), sets[0][5].cpu())})
+        del sets, first
+    # what a launch costs before it moves a byte: an empty-handed kernel, same graph structure
+    x = torch.zeros(1, device=dev)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        for _ in range(200):
+            x.add_(1.0)
+    g.replay()
+    fence()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    g.replay()
+    t1.record()
+    torch.cuda.synchronize()
+    floor = 1e3 * t0.elapsed_time(t1) / 200
+    for row in rows:
+        row["launch_floor_us"] = floor
+    return rows
+
+
+def check_small_workloads(rows):
+    """Parity bit per small workload: this run's output against the CPU oracle (bitwise for
+    the serial kernels, |a-b| <= max(1e-6, 1e-5|b|) for the scan kernel)."""
+    import numpy as np
+    from oracle import puff_oracle
+    for row in rows:
+        wl, got, sums = row["_got"]
+        inputs = [t.numpy() for t in make_inputs(wl)]
+        want = np.zeros(inputs[0].shape, dtype=np.float32)
+        puff_oracle.advantage(*inputs, want, *wl.hyper())
+        got = got.numpy()
+        if row["kernel"] == "scan":
+            ok = bool(np.all(np.abs(got - want) <= np.maximum(1e-6, 1e-5 * np.abs(want))))
+            row["parity"] = "within 1e-5 rel / 1e-6 abs of the oracle" if ok else "FAILED"
+        else:
+            ok = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+            row["parity"] = "bitwise equal to the oracle" if ok else "FAILED"
+        exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
+        row["sums_ok"] = bool(np.allclose(sums.numpy(), exact, rtol=1e-5, atol=1e-6))
 
 
 def time_reference_cuda_kernel(sets, n_sets, hyper, elems):
@@ -610,12 +842,13 @@ def run_sequence_arm(args, wl):
                 "reference_style = torch.zeros + this repo's 9-argument op + the reference's eager torch lines"}), flush=True)
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant
-# kernel from the ncu capture summarised in
-# profiles/tma2d_ws_kernel_cfg2_32768x256_ncu_full.md: 138.45 MB read + 15.64 MB written
-# on a 32768-segment case, scaled by the rows of a full launch (every row is read once,
-# so traffic grows in proportion).
-TRAFFIC = {("cfg2", "tma2d"): int((138.45e6 + 14.79e6) * 4)}
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum, dram__bytes_write.sum)
+# from the ncu capture summarised under profiles/ (see `source`), keyed by workload and kernel.
+TRAFFIC = {
+    ("cfg2", "tma2d"): {"read": 4 * 138.45e6, "write": 4 * 14.79e6,
+                        "source": "profiles/tma2d_ws_kernel_cfg2_32768x256_ncu_full.md: a 32768-segment capture x 4; "
+                                  "its 33.5 MB output stayed partly in L2, so the write figure is a lower bound"},
+}
 
 
 def main():
@@ -630,8 +863,13 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--sequence", action="store_true",
                     help="time the trainer's per-minibatch sequence (eager reference lines vs fused entry points)")
-    ap.add_argument("--no-overlap", action="store_true",
-                    help="run the priority launches and the all-reduce on the kernel's stream")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="N > 1: how the weight total crosses GPUs (peer stores inside the priority kernels, "
+                         "or a torch.distributed all-reduce between them)")
+    ap.add_argument("--reserve-sms", type=int, default=0,
+                    help="SMs the persistent advantage grid leaves free for side-stream kernels")
+    ap.add_argument("--no-strong", action="store_true", help="N > 1: skip the strong-scaling leg")
+    ap.add_argument("--no-small", action="store_true", help="N = 1: skip the small-workload table")
     ap.add_argument("--no-graph", action="store_true", help="never capture the timed loop into CUDA graphs")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference CUDA kernel")
     ap.add_argument("--segments", type=int, default=0,

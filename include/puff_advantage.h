@@ -130,6 +130,14 @@ int puff_advantage_sm100_host(const float* h_values, const float* h_rewards,
                               long long num_segments, long long horizon,
                               int variant, int device);
 int puff_advantage_sm100_host_release(int device);
+/* The copies of puff_advantage_sm100_host without its kernels: same blocks,
+ * same streams, same bytes in both directions, nothing computed (h_advantages
+ * receives whatever the staging buffers hold).  For benchmarks: the time the
+ * host-buffer path cannot go below on a given machine. */
+int puff_advantage_sm100_host_copies_only(const float* h_values, const float* h_rewards,
+                                          const float* h_dones, const float* h_importance,
+                                          float* h_advantages, float* h_seg_abs_sum,
+                                          long long num_segments, long long horizon, int device);
 
 /*
  * Prioritised-replay weights from the fused per-segment sums, on DEVICE
@@ -154,6 +162,59 @@ int puff_priorities_sm100_weights(const float* seg_abs_sum, float* weights,
 int puff_priorities_sm100_probs(const float* weights, const double* total_w,
                                 float* probs, long long num_segments,
                                 void* cuda_stream);
+
+/*
+ * The same two steps for segments sharded over several GPUs, with the exchange
+ * of the weight total done by the kernels themselves instead of a collective
+ * library call between them.  (The reference never shards this op: its DDP
+ * ranks own private buffers, pufferl.py:913-939, and the only torch.distributed
+ * calls near it are 1-element all-reduces for logging, pufferl.py:708-714.
+ * This is the layout of the multi-GPU benchmark: contiguous row blocks per
+ * rank, one process per GPU or one process driving several.)
+ *
+ * A puff_exchange is one rank's end of the exchange: a mailbox of a few hundred
+ * bytes in that rank's device memory that every other rank can store into.
+ *   _create   allocates it on the current device (set-up time; this is the only
+ *             allocation) and, when handle_out is non-NULL, fills it with
+ *             PUFF_EXCHANGE_HANDLE_BYTES bytes that identify the mailbox to
+ *             other PROCESSES on the same machine (a CUDA IPC handle).
+ *   _connect  takes the handles of all `world` ranks, indexed by rank, as one
+ *             array of world * PUFF_EXCHANGE_HANDLE_BYTES bytes (exchange them
+ *             with whatever the host program has: torch.distributed, MPI, a
+ *             file) and maps the peers' mailboxes.
+ *   _connect_pointers  the same for ranks that live in ONE process: device
+ *             pointers from puff_exchange_sm100_mailbox(), indexed by rank
+ *             (peer access between the devices must be enabled by the caller).
+ *   _set_wait_ns  the bound of the in-kernel wait (default 2 s).
+ *   _destroy  synchronises the device and frees everything.
+ *
+ *   puff_priorities_sm100_weights_push   weights[s] as puff_priorities_sm100_weights,
+ *             then the local fp64 total is stored into every rank's mailbox
+ *             (plain stores over NVLink to peer-mapped memory, fence, flag).
+ *   puff_priorities_sm100_probs_gathered  waits until all `world` totals of the
+ *             current round sit in this rank's own mailbox, adds them in rank
+ *             order (identical on every rank), writes the global total to
+ *             *total_w (nullable) and probs[s] = (weights[s] + 1e-6) / (total + 1e-6).
+ * Every rank must issue the same sequence of _weights_push / _probs_gathered
+ * pairs, each rank on one stream.  A rank with num_segments == 0 still takes
+ * part.  The wait is bounded: when a peer's total has not arrived in time the
+ * kernel records PUFF_ERR_DEVICE_WAIT in the device status word
+ * (puff_advantage_sm100_device_status) and returns without writing probs.
+ */
+#define PUFF_EXCHANGE_HANDLE_BYTES 64
+typedef struct puff_exchange puff_exchange;
+int puff_exchange_sm100_create(int rank, int world, void* handle_out, puff_exchange** exchange);
+int puff_exchange_sm100_connect(puff_exchange* exchange, const void* all_handles);
+int puff_exchange_sm100_connect_pointers(puff_exchange* exchange, void* const* mailboxes);
+void* puff_exchange_sm100_mailbox(puff_exchange* exchange);
+int puff_exchange_sm100_set_wait_ns(puff_exchange* exchange, unsigned long long wait_ns);
+int puff_exchange_sm100_destroy(puff_exchange* exchange);
+int puff_priorities_sm100_weights_push(const float* seg_abs_sum, float* weights, float alpha,
+                                       long long num_segments, void* scratch, size_t scratch_bytes,
+                                       puff_exchange* exchange, void* cuda_stream);
+int puff_priorities_sm100_probs_gathered(const float* weights, double* total_w, float* probs,
+                                         long long num_segments, puff_exchange* exchange,
+                                         void* cuda_stream);
 
 /*
  * Minibatch gather and advantage normalisation, on DEVICE buffers, asynchronous
@@ -270,7 +331,8 @@ int puff_advantage_sm100_inject_status(int value);
 #define PUFF_TUNE_CTAS_PER_SM   3   /* PUFF_ADV_CTAS_PER_SM: cap on resident CTAs per SM of the tma2d kernels */
 #define PUFF_TUNE_LOAD_GROUP    4   /* PUFF_ADV_GROUP: chunks whose loads the warp-specialised producer issues together */
 #define PUFF_TUNE_SCAN_THREADS  5   /* PUFF_ADV_SCAN_THREADS: threads per row of the scan kernel (power of two, 32..1024) */
-#define PUFF_TUNE_COUNT         6
+#define PUFF_TUNE_RESERVE_SMS   6   /* PUFF_ADV_RESERVE_SMS: SMs the persistent (warp-specialised) grids leave free for other streams' kernels */
+#define PUFF_TUNE_COUNT         7
 int puff_advantage_sm100_set_tuning(int knob, int value);
 /* Library version, "major.minor". */
 const char* puff_advantage_sm100_version(void);

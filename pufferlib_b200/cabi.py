@@ -18,6 +18,7 @@ OK = 0
 ERR_NULL, ERR_SHAPE, ERR_VARIANT, ERR_ALIGN, ERR_ALIAS = -1, -2, -3, -4, -5
 ERR_ARCH, ERR_DRIVER, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_SIZE = -6, -7, -8, -9, -10
 NOALLOC_MAX_SEGMENTS = 524288
+EXCHANGE_HANDLE_BYTES = 64
 FLAG_ZERO_LAST_COLUMN = 1
 VARIANT_AUTO, VARIANT_SERIAL, VARIANT_SCAN, VARIANT_GENERIC = 0, 1, 2, 3
 KERNEL_NONE, KERNEL_TMA2D, KERNEL_BULK1D, KERNEL_SCAN, KERNEL_GENERIC = 0, 1, 2, 3, 4
@@ -35,9 +36,18 @@ SIGNATURES = {
     "puff_advantage_sm100_launch_ex": (_I, [_P] * 6 + [_F] * 4 + [_LL, _LL, _I, ctypes.c_uint, _P]),
     "puff_advantage_sm100_host": (_I, [_P] * 6 + [_F] * 4 + [_LL, _LL, _I, _I]),
     "puff_advantage_sm100_host_release": (_I, [_I]),
+    "puff_advantage_sm100_host_copies_only": (_I, [_P] * 6 + [_LL, _LL, _I]),
     "puff_priorities_sm100_scratch_bytes": (ctypes.c_size_t, [_LL]),
     "puff_priorities_sm100_weights": (_I, [_P, _P, _P, _F, _LL, _P, ctypes.c_size_t, _P]),
     "puff_priorities_sm100_probs": (_I, [_P, _P, _P, _LL, _P]),
+    "puff_exchange_sm100_create": (_I, [_I, _I, _P, ctypes.POINTER(_P)]),
+    "puff_exchange_sm100_connect": (_I, [_P, _P]),
+    "puff_exchange_sm100_connect_pointers": (_I, [_P, ctypes.POINTER(_P)]),
+    "puff_exchange_sm100_mailbox": (_P, [_P]),
+    "puff_exchange_sm100_set_wait_ns": (_I, [_P, ctypes.c_ulonglong]),
+    "puff_exchange_sm100_destroy": (_I, [_P]),
+    "puff_priorities_sm100_weights_push": (_I, [_P, _P, _F, _LL, _P, ctypes.c_size_t, _P, _P]),
+    "puff_priorities_sm100_probs_gathered": (_I, [_P, _P, _P, _LL, _P, _P]),
     "puff_minibatch_sm100_scratch_bytes": (ctypes.c_size_t, [_LL]),
     "puff_minibatch_sm100_gather": (_I, [_P] * 9 + [_F, _LL, _LL, _LL, _P, ctypes.c_size_t, _P]),
     "puff_minibatch_sm100_gather_ex": (_I, [_P] * 9 + [_F, _LL, _LL, _LL, _LL, _P, ctypes.c_size_t, _P]),
@@ -73,7 +83,8 @@ def load():
     return _lib
 
 
-TUNE = {"force_kernel": 0, "stages": 1, "ws_stages": 2, "ctas_per_sm": 3, "load_group": 4, "scan_threads": 5}
+TUNE = {"force_kernel": 0, "stages": 1, "ws_stages": 2, "ctas_per_sm": 3, "load_group": 4, "scan_threads": 5,
+        "reserve_sms": 6}
 
 
 def set_tuning(**knobs):

@@ -222,7 +222,7 @@ static void tune_init()
     std::call_once(g_tune_once, [] {
         static const char* const names[PUFF_TUNE_COUNT] = {"PUFF_ADV_FORCE_KERNEL", "PUFF_ADV_STAGES", "PUFF_ADV_WS",
                                                            "PUFF_ADV_CTAS_PER_SM", "PUFF_ADV_GROUP",
-                                                           "PUFF_ADV_SCAN_THREADS"};
+                                                           "PUFF_ADV_SCAN_THREADS", "PUFF_ADV_RESERVE_SMS"};
         for (int i = 0; i < PUFF_TUNE_COUNT; ++i) {
             const char* v = getenv(names[i]);
             g_tune[i].store((v != nullptr && *v != '\0') ? atoi(v) : -1, std::memory_order_relaxed);
@@ -235,6 +235,16 @@ static int tune(int knob, int fallback)
     tune_init();
     const int v = g_tune[knob].load(std::memory_order_relaxed);
     return v < 0 ? fallback : v;
+}
+
+// SMs a persistent (warp-specialised) grid is sized for: all of them, minus the few that
+// PUFF_TUNE_RESERVE_SMS leaves free for kernels of other streams that must not wait for the
+// whole persistent grid to retire (a collective's kernel, for instance)
+static int persistent_sms(int sm_count)
+{
+    const int r = tune(PUFF_TUNE_RESERVE_SMS, 0);
+    const int n = sm_count - (r < 0 ? 0 : r);
+    return n < 1 ? 1 : n;
 }
 
 template <int NST>
@@ -466,7 +476,7 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
                 if (per_sm > 2) per_sm = 2;
                 { const int o = tune(PUFF_TUNE_CTAS_PER_SM, 0); if (o > 0) per_sm = o < 3 ? o : 3; }
                 if (per_sm < 1) per_sm = 1;
-                const long long mg = static_cast<long long>(dev->sm_count) * per_sm;
+                const long long mg = static_cast<long long>(persistent_sms(dev->sm_count)) * per_sm;
                 const int grid = static_cast<int>(tiles < mg ? tiles : mg);
 #define PUFF_WS_CASE(A, B) err = launch_tma2d_ws<A, B>(cache, zero_last ? nullptr : p[4], abs_p, gamma, lambda, rho_clip, c_clip, rows, static_cast<int>(horizon), grid, static_cast<int>(tiles), st)
                 if (wnst == 2) PUFF_WS_CASE(2, 2);
@@ -500,7 +510,7 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
         const int use_ws = ws_rows > 0 ? tune(PUFF_TUNE_WS_STAGES, ws_tiles >= 8LL * dev->sm_count ? 1 : 0) : 0;
         if (use_ws != 0) {
             const long long tiles = (num_segments + ws_rows - 1) / ws_rows;
-            const long long max_grid = dev->sm_count;
+            const long long max_grid = persistent_sms(dev->sm_count);
             const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
             puff_adv_bulk1d_ws_kernel<<<grid, kB1wThreads, ws_smem, st>>>(values, rewards, dones, importance, advantages,
                                                                          seg_abs_sum, gamma, lambda, rho_clip, c_clip,
@@ -583,6 +593,15 @@ void count_launch() { g_launch_count.fetch_add(1, std::memory_order_relaxed); }
 }
 
 namespace puff {
+// Device address of the status word on the current device (nullptr on failure), for kernels of
+// other translation units that report into the same word.
+int* device_status_ptr()
+{
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+    return static_cast<int*>(p);
+}
+
 // Reads (and, when set, clears) the status word of the current device.  The caller has already
 // synchronised the streams whose kernels it asks about.
 int take_device_status()

@@ -72,10 +72,10 @@ static long long env_ll(const char* name, long long fallback)
 
 using namespace puff;
 
-extern "C" int puff_advantage_sm100_host(const float* h_values, const float* h_rewards, const float* h_dones,
-                                         const float* h_importance, float* h_advantages, float* h_seg_abs_sum,
-                                         float gamma, float lambda, float rho_clip, float c_clip,
-                                         long long num_segments, long long horizon, int variant, int device)
+static int host_pipeline(const float* h_values, const float* h_rewards, const float* h_dones,
+                         const float* h_importance, float* h_advantages, float* h_seg_abs_sum,
+                         float gamma, float lambda, float rho_clip, float c_clip,
+                         long long num_segments, long long horizon, int variant, int device, bool compute)
 {
     if (num_segments < 0 || horizon < 0) return PUFF_ERR_SHAPE;
     if (variant < PUFF_VARIANT_AUTO || variant > PUFF_VARIANT_GENERIC) return PUFF_ERR_VARIANT;
@@ -141,8 +141,9 @@ extern "C" int puff_advantage_sm100_host(const float* h_values, const float* h_r
             for (int a = 0; a < 4 && e == cudaSuccess; ++a)
                 e = cudaMemcpyAsync(d_in[a], h_in[a] + off, n * sizeof(float), cudaMemcpyHostToDevice, st);
             if (e != cudaSuccess) { rc = static_cast<int>(e); break; }
-            rc = puff_advantage_sm100_launch(d_in[0], d_in[1], d_in[2], d_in[3], d_adv, d_abs, gamma, lambda,
-                                             rho_clip, c_clip, rows, horizon, variant, st);
+            if (compute)
+                rc = puff_advantage_sm100_launch(d_in[0], d_in[1], d_in[2], d_in[3], d_adv, d_abs, gamma, lambda,
+                                                 rho_clip, c_clip, rows, horizon, variant, st);
             if (rc != PUFF_OK) break;
             e = cudaMemcpy2DAsync(h_advantages + off, horizon * sizeof(float), d_adv, horizon * sizeof(float),
                                   (horizon - 1) * sizeof(float), rows, cudaMemcpyDeviceToHost, st);
@@ -160,6 +161,24 @@ extern "C" int puff_advantage_sm100_host(const float* h_values, const float* h_r
     }
     cudaSetDevice(prev);
     return rc;
+}
+
+extern "C" int puff_advantage_sm100_host(const float* h_values, const float* h_rewards, const float* h_dones,
+                                         const float* h_importance, float* h_advantages, float* h_seg_abs_sum,
+                                         float gamma, float lambda, float rho_clip, float c_clip,
+                                         long long num_segments, long long horizon, int variant, int device)
+{
+    return host_pipeline(h_values, h_rewards, h_dones, h_importance, h_advantages, h_seg_abs_sum, gamma, lambda,
+                         rho_clip, c_clip, num_segments, horizon, variant, device, true);
+}
+
+extern "C" int puff_advantage_sm100_host_copies_only(const float* h_values, const float* h_rewards,
+                                                     const float* h_dones, const float* h_importance,
+                                                     float* h_advantages, float* h_seg_abs_sum,
+                                                     long long num_segments, long long horizon, int device)
+{
+    return host_pipeline(h_values, h_rewards, h_dones, h_importance, h_advantages, h_seg_abs_sum, 0.f, 0.f, 0.f, 0.f,
+                         num_segments, horizon, PUFF_VARIANT_AUTO, device, false);
 }
 
 extern "C" int puff_advantage_sm100_host_release(int device)

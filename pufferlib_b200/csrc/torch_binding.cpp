@@ -199,6 +199,42 @@ torch::Tensor puff_priority_probs_cuda(torch::Tensor weights, torch::Tensor tota
     return probs;
 }
 
+// The two priority steps of a sharded buffer with the exchange of the weight total done by the
+// kernels (include/puff_advantage.h, puff_exchange).  `exchange` is the puff_exchange* as an integer.
+torch::Tensor puff_priority_weights_push_cuda(torch::Tensor seg_abs_sum, double alpha, int64_t exchange)
+{
+    TORCH_CHECK(seg_abs_sum.is_cuda(), "All tensors must be on GPU");
+    TORCH_CHECK(seg_abs_sum.dim() == 1 && seg_abs_sum.dtype() == torch::kFloat32 && seg_abs_sum.is_contiguous(),
+                "seg_abs_sum must be a contiguous 1D float32 tensor");
+    const c10::cuda::CUDAGuard guard(seg_abs_sum.device());
+    const int64_t n = seg_abs_sum.size(0);
+    auto weights = torch::empty_like(seg_abs_sum);
+    const size_t sbytes = puff_priorities_sm100_scratch_bytes(n);
+    auto scratch = torch::empty({static_cast<int64_t>((sbytes + 7) / 8)}, seg_abs_sum.options().dtype(torch::kFloat64));
+    const int rc = puff_priorities_sm100_weights_push(seg_abs_sum.data_ptr<float>(), weights.data_ptr<float>(),
+                                                      static_cast<float>(alpha), n, scratch.data_ptr<double>(), sbytes,
+                                                      reinterpret_cast<puff_exchange*>(exchange),
+                                                      at::cuda::getCurrentCUDAStream().stream());
+    check_rc(rc, "puff_priority_weights_push");
+    return weights;
+}
+
+std::tuple<torch::Tensor, torch::Tensor> puff_priority_probs_gathered_cuda(torch::Tensor weights, int64_t exchange)
+{
+    TORCH_CHECK(weights.is_cuda(), "All tensors must be on GPU");
+    TORCH_CHECK(weights.dim() == 1 && weights.dtype() == torch::kFloat32 && weights.is_contiguous(),
+                "weights must be a contiguous 1D float32 tensor");
+    const c10::cuda::CUDAGuard guard(weights.device());
+    auto probs = torch::empty_like(weights);
+    auto total = torch::empty({1}, weights.options().dtype(torch::kFloat64));
+    const int rc = puff_priorities_sm100_probs_gathered(weights.data_ptr<float>(), total.data_ptr<double>(),
+                                                        probs.data_ptr<float>(), weights.size(0),
+                                                        reinterpret_cast<puff_exchange*>(exchange),
+                                                        at::cuda::getCurrentCUDAStream().stream());
+    check_rc(rc, "puff_priority_probs_gathered");
+    return {probs, total};
+}
+
 // pufferl.py:363, 373-375, 408-409 for sampled segment indices.
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor>
 puff_minibatch_gather_cuda(torch::Tensor advantages, torch::Tensor values, torch::Tensor prio_probs,
@@ -287,6 +323,11 @@ std::tuple<torch::Tensor, torch::Tensor> puff_priority_weights_meta(torch::Tenso
     return {torch::empty_like(seg_abs_sum), torch::empty({1}, seg_abs_sum.options().dtype(torch::kFloat64))};
 }
 torch::Tensor puff_priority_probs_meta(torch::Tensor weights, torch::Tensor) { return torch::empty_like(weights); }
+torch::Tensor puff_priority_weights_push_meta(torch::Tensor seg_abs_sum, double, int64_t) { return torch::empty_like(seg_abs_sum); }
+std::tuple<torch::Tensor, torch::Tensor> puff_priority_probs_gathered_meta(torch::Tensor weights, int64_t)
+{
+    return {torch::empty_like(weights), torch::empty({1}, weights.options().dtype(torch::kFloat64))};
+}
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor>
 puff_minibatch_gather_meta(torch::Tensor advantages, torch::Tensor, torch::Tensor, torch::Tensor idx, double, int64_t)
 {
@@ -305,6 +346,8 @@ TORCH_LIBRARY(pufferlib, m)
     m.def("puff_set_variant(int variant) -> int", &puff_set_variant);
     m.def("puff_priority_weights(Tensor seg_abs_sum, float alpha) -> (Tensor, Tensor)");
     m.def("puff_priority_probs(Tensor weights, Tensor total_w) -> Tensor");
+    m.def("puff_priority_weights_push(Tensor seg_abs_sum, float alpha, int exchange) -> Tensor");
+    m.def("puff_priority_probs_gathered(Tensor weights, int exchange) -> (Tensor, Tensor)");
     m.def("puff_rollout_write(Tensor(a!) rewards, Tensor(b!) terminals, Tensor(c!) values, Tensor step_rewards, Tensor step_dones, Tensor step_values, int row_begin, int column, float reward_clip) -> ()");
     m.def("puff_minibatch_gather(Tensor advantages, Tensor values, Tensor prio_probs, Tensor idx, float anneal_beta, int prio_segments=-1) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
 }
@@ -316,6 +359,8 @@ TORCH_LIBRARY_IMPL(pufferlib, CUDA, m)
     m.impl("compute_puff_advantage_fill", &compute_puff_advantage_fill_cuda);
     m.impl("puff_priority_weights", &puff_priority_weights_cuda);
     m.impl("puff_priority_probs", &puff_priority_probs_cuda);
+    m.impl("puff_priority_weights_push", &puff_priority_weights_push_cuda);
+    m.impl("puff_priority_probs_gathered", &puff_priority_probs_gathered_cuda);
     m.impl("puff_minibatch_gather", &puff_minibatch_gather_cuda);
     m.impl("puff_rollout_write", &puff_rollout_write_cuda);
 }
@@ -328,6 +373,8 @@ TORCH_LIBRARY_IMPL(pufferlib, Meta, m)
     m.impl("puff_rollout_write", &puff_rollout_write_meta);
     m.impl("puff_priority_weights", &puff_priority_weights_meta);
     m.impl("puff_priority_probs", &puff_priority_probs_meta);
+    m.impl("puff_priority_weights_push", &puff_priority_weights_push_meta);
+    m.impl("puff_priority_probs_gathered", &puff_priority_probs_gathered_meta);
     m.impl("puff_minibatch_gather", &puff_minibatch_gather_meta);
 }
 

@@ -2,8 +2,10 @@
 
 Segments (rows) are independent, so a buffer of `segments x horizon` shards by
 contiguous row blocks with no data-path communication; the only exchange is
-the all-reduce of one fp64 scalar, the total priority weight that
-pufferl.py:361 divides by.  The reference itself never shards this op (its DDP
+one fp64 scalar per rank, the total priority weight that pufferl.py:361
+divides by: either all-reduced by torch.distributed between the two priority
+launches, or (with a `PeerExchange`) stored by the priority kernels straight
+into every peer's memory.  The reference itself never shards this op (its DDP
 ranks own private buffers, pufferl.py:913-939); this class is the layout the
 multi-GPU benchmark measures: one process per GPU, `torch.distributed` for
 the scalar.
@@ -44,8 +46,11 @@ class ShardedAdvantage:
     globally normalised sampling probabilities."""
 
     def __init__(self, global_segments, horizon, hyper, prio_alpha, group=None, kernels=None,
-                 rank=None, world=None):
+                 rank=None, world=None, exchange=None):
         self.group = group
+        # exchange: a pufferlib_b200.exchange.PeerExchange -> the weight total crosses GPUs inside
+        # the priority kernels; None -> torch.distributed all-reduce between them
+        self.exchange = exchange
         if rank is None:
             rank = dist.get_rank(group) if dist.is_initialized() else 0
         if world is None:
@@ -64,6 +69,9 @@ class ShardedAdvantage:
 
     def priorities(self, seg_abs_sum):
         """Local weights, their all-reduced total, globally normalised probabilities."""
+        if self.exchange is not None:
+            weights = self.exchange.weights_push(seg_abs_sum, self.prio_alpha)
+            return self.exchange.probs_gathered(weights)
         k = self.kernels
         weights, total = k.weights(seg_abs_sum, self.prio_alpha)
         if self.world > 1:
