@@ -845,9 +845,10 @@ def run_sequence_arm(args, wl):
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum, dram__bytes_write.sum)
 # from the ncu capture summarised under profiles/ (see `source`), keyed by workload and kernel.
 TRAFFIC = {
-    ("cfg2", "tma2d"): {"read": 4 * 138.45e6, "write": 4 * 14.79e6,
-                        "source": "profiles/tma2d_ws_kernel_cfg2_32768x256_ncu_full.md: a 32768-segment capture x 4; "
-                                  "its 33.5 MB output stayed partly in L2, so the write figure is a lower bound"},
+    ("cfg2", "tma2d"): {"read": 553692928, "write": 115028992,
+                        "source": "profiles/tma2d_ws_kernel_cfg2_131072x256_dram_traffic.md: one full-size launch; "
+                                  "about 20 MB of the 134 MB output is still dirty in L2 when the kernel ends, "
+                                  "so writes read below the algorithmic 134.2 MB"},
 }
 
 
