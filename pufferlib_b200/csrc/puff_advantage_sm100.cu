@@ -222,7 +222,8 @@ static void tune_init()
     std::call_once(g_tune_once, [] {
         static const char* const names[PUFF_TUNE_COUNT] = {"PUFF_ADV_FORCE_KERNEL", "PUFF_ADV_STAGES", "PUFF_ADV_WS",
                                                            "PUFF_ADV_CTAS_PER_SM", "PUFF_ADV_GROUP",
-                                                           "PUFF_ADV_SCAN_THREADS", "PUFF_ADV_RESERVE_SMS"};
+                                                           "PUFF_ADV_SCAN_THREADS", "PUFF_ADV_RESERVE_SMS",
+                                                           "PUFF_ADV_TILE_ROWS", "PUFF_ADV_PDL"};
         for (int i = 0; i < PUFF_TUNE_COUNT; ++i) {
             const char* v = getenv(names[i]);
             g_tune[i].store((v != nullptr && *v != '\0') ? atoi(v) : -1, std::memory_order_relaxed);
@@ -247,19 +248,37 @@ static int persistent_sms(int sm_count)
     return n < 1 ? 1 : n;
 }
 
+// Every advantage kernel is launched with the programmatic-stream-serialization attribute (unless
+// PUFF_TUNE_PDL is 0): its set-up may then overlap the tail of whatever precedes it in the stream,
+// and it waits (pdl_wait in the kernels) for that predecessor to complete before it touches a tensor.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st,
+                                 Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(block));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tune(PUFF_TUNE_PDL, 1) != 0 ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <int NST>
 static cudaError_t launch_tma2d(const MapSet& m, const float* adv_in, float* seg_abs_sum, float gamma, float lambda, float rho_clip,
                                 float c_clip, long long rows, int horizon, int grid, int tiles, cudaStream_t st)
 {
     if (seg_abs_sum != nullptr)
-        puff_adv_tma2d_kernel<NST, true><<<grid, 32, tma2d_smem_bytes<NST>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], adv_in, seg_abs_sum, gamma, lambda, rho_clip, c_clip,
-            rows, horizon, tiles);
-    else
-        puff_adv_tma2d_kernel<NST, false><<<grid, 32, tma2d_smem_bytes<NST>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], adv_in, nullptr, gamma, lambda, rho_clip, c_clip,
-            rows, horizon, tiles);
-    return cudaGetLastError();
+        return launch_kernel(puff_adv_tma2d_kernel<NST, true>, grid, 32, tma2d_smem_bytes<NST>(), st,
+                             m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], adv_in, seg_abs_sum, gamma, lambda, rho_clip,
+                             c_clip, rows, horizon, tiles);
+    return launch_kernel(puff_adv_tma2d_kernel<NST, false>, grid, 32, tma2d_smem_bytes<NST>(), st,
+                         m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], adv_in, static_cast<float*>(nullptr), gamma, lambda,
+                         rho_clip, c_clip, rows, horizon, tiles);
 }
 
 template <int NST, int NT>
@@ -269,14 +288,12 @@ static cudaError_t launch_tma2d_ws(const MapSet& m, const float* adv_in, float* 
     int group = tune(PUFF_TUNE_LOAD_GROUP, NST % 2 == 0 ? 2 : 1);
     if (group < 1 || NST % group != 0) group = 1;
     if (seg_abs_sum != nullptr)
-        puff_adv_tma2d_ws_kernel<NST, NT, true><<<grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[0], m.ptr[1], m.ptr[2], m.ptr[3], adv_in, seg_abs_sum, gamma, lambda, rho_clip, c_clip,
-            rows, horizon, tiles, group);
-    else
-        puff_adv_tma2d_ws_kernel<NST, NT, false><<<grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st>>>(
-            m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[0], m.ptr[1], m.ptr[2], m.ptr[3], adv_in, nullptr, gamma, lambda, rho_clip, c_clip,
-            rows, horizon, tiles, group);
-    return cudaGetLastError();
+        return launch_kernel(puff_adv_tma2d_ws_kernel<NST, NT, true>, grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st,
+                             m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[0], m.ptr[1], m.ptr[2], m.ptr[3], adv_in,
+                             seg_abs_sum, gamma, lambda, rho_clip, c_clip, rows, horizon, tiles, group);
+    return launch_kernel(puff_adv_tma2d_ws_kernel<NST, NT, false>, grid, kWsThreads, tma2d_ws_smem_bytes<NST, NT>(), st,
+                         m.tm[0], m.tm[1], m.tm[2], m.tm[3], m.tm[4], m.ptr[0], m.ptr[1], m.ptr[2], m.ptr[3], adv_in,
+                         static_cast<float*>(nullptr), gamma, lambda, rho_clip, c_clip, rows, horizon, tiles, group);
 }
 
 static bool ranges_overlap(const void* a, size_t na, const void* b, size_t nb)
@@ -291,7 +308,9 @@ static bool ranges_overlap(const void* a, size_t na, const void* b, size_t nb)
 static int bulk1d_tile_rows(long long horizon, int max_smem, size_t* smem_bytes)
 {
     const int cand[4] = {32, 16, 8, 4};
+    const int cap = tune(PUFF_TUNE_TILE_ROWS, 32);
     for (int i = 0; i < 4; ++i) {
+        if (cand[i] > cap && cand[i] > 4) continue;
         if (static_cast<long long>(cand[i]) * horizon > kB1MaxElems) continue;
         const size_t arr = (static_cast<size_t>(cand[i]) * horizon * 4 + 15) & ~static_cast<size_t>(15);
         const size_t need = 4 * arr + 16 + 128;
@@ -308,7 +327,9 @@ static int bulk1d_tile_rows(long long horizon, int max_smem, size_t* smem_bytes)
 static int bulk1d_ws_tile_rows(long long horizon, int max_smem, size_t* smem_bytes)
 {
     const int cand[4] = {32, 16, 8, 4};
+    const int cap = tune(PUFF_TUNE_TILE_ROWS, 32);
     for (int i = 0; i < 4; ++i) {
+        if (cand[i] > cap && cand[i] > 4) continue;
         const size_t arr = (static_cast<size_t>(cand[i]) * horizon * 4 + 15) & ~static_cast<size_t>(15);
         const size_t need = (kB1wStages * 4 + kB1wTerms * 2) * arr + 8 * (2 * kB1wStages + 2 * kB1wTerms) + 4 * kB1wTerms + 64 + 128;
         if (need > static_cast<size_t>(max_smem)) continue;
@@ -512,21 +533,19 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             const long long tiles = (num_segments + ws_rows - 1) / ws_rows;
             const long long max_grid = persistent_sms(dev->sm_count);
             const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
-            puff_adv_bulk1d_ws_kernel<<<grid, kB1wThreads, ws_smem, st>>>(values, rewards, dones, importance, advantages,
-                                                                         seg_abs_sum, gamma, lambda, rho_clip, c_clip,
-                                                                         num_segments, static_cast<int>(horizon), ws_rows,
-                                                                         tiles, zero_last);
+            err = launch_kernel(puff_adv_bulk1d_ws_kernel, grid, kB1wThreads, ws_smem, st, values, rewards, dones,
+                                importance, advantages, seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments,
+                                static_cast<int>(horizon), ws_rows, tiles, zero_last);
         } else {
         const long long tiles = (num_segments + bulk_rows - 1) / bulk_rows;
         int per_sm = static_cast<int>(static_cast<size_t>(dev->max_smem_optin + 1024) / (bulk_smem + 1024));
         per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
         const long long max_grid = static_cast<long long>(dev->sm_count) * per_sm;
         const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
-        puff_adv_bulk1d_kernel<<<grid, kB1Threads, bulk_smem, st>>>(values, rewards, dones, importance, advantages,
-                                                                    seg_abs_sum, gamma, lambda, rho_clip, c_clip,
-                                                                    num_segments, static_cast<int>(horizon), bulk_rows, tiles, zero_last);
+        err = launch_kernel(puff_adv_bulk1d_kernel, grid, kB1Threads, bulk_smem, st, values, rewards, dones, importance,
+                            advantages, seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments,
+                            static_cast<int>(horizon), bulk_rows, tiles, zero_last);
         }
-        err = cudaGetLastError();
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
     } else if (kernel == PUFF_KERNEL_SCAN) {
         const long long units = (horizon + 3) / 4;
@@ -541,20 +560,18 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
         const long long max_grid = static_cast<long long>(dev->sm_count) * (2048 / nt) ;
         const int grid = static_cast<int>(num_segments < max_grid ? num_segments : max_grid);
         if (aligned16 && horizon % 4 == 0)
-            puff_adv_scan_kernel<true><<<grid, nt, 0, st>>>(values, rewards, dones, importance, advantages, seg_abs_sum,
-                                                            gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon), zero_last);
+            err = launch_kernel(puff_adv_scan_kernel<true>, grid, nt, 0, st, values, rewards, dones, importance, advantages,
+                                seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon), zero_last);
         else
-            puff_adv_scan_kernel<false><<<grid, nt, 0, st>>>(values, rewards, dones, importance, advantages, seg_abs_sum,
-                                                             gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon), zero_last);
-        err = cudaGetLastError();
+            err = launch_kernel(puff_adv_scan_kernel<false>, grid, nt, 0, st, values, rewards, dones, importance, advantages,
+                                seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon), zero_last);
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
     } else {
         const long long blocks = (num_segments + 127) / 128;
         const long long max_grid = static_cast<long long>(dev->sm_count) * 16;
         const int grid = static_cast<int>(blocks < max_grid ? blocks : max_grid);
-        puff_adv_generic_kernel<<<grid, 128, 0, st>>>(values, rewards, dones, importance, advantages, seg_abs_sum,
-                                                      gamma, lambda, rho_clip, c_clip, num_segments, horizon, zero_last);
-        err = cudaGetLastError();
+        err = launch_kernel(puff_adv_generic_kernel, grid, 128, 0, st, values, rewards, dones, importance, advantages,
+                            seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments, horizon, zero_last);
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
     }
     t_last_kernel = kernel;
@@ -628,6 +645,19 @@ extern "C" int puff_advantage_sm100_inject_status(int value)
 {
     return static_cast<int>(cudaMemcpyToSymbol(g_device_status, &value, sizeof(int)));
 }
+
+#ifdef PUFF_TIMELINE
+// Debug builds only: copies the per-CTA phase stamps (kTimelineSlots per CTA, nanoseconds of
+// %globaltimer) of the most recent instrumented launch into `out`.
+extern "C" int puff_advantage_sm100_timeline(unsigned long long* out, int ctas)
+{
+    if (ctas > kTimelineCtas) ctas = kTimelineCtas;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess)
+        e = cudaMemcpyFromSymbol(out, g_timeline, sizeof(unsigned long long) * kTimelineSlots * ctas);
+    return static_cast<int>(e);
+}
+#endif
 
 extern "C" int puff_advantage_sm100_set_tuning(int knob, int value)
 {

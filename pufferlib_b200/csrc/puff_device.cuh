@@ -14,6 +14,25 @@ namespace puff {
 // Device-side status word: PUFF_ERR_DEVICE_WAIT when a bounded wait gave up.
 __device__ int g_device_status = 0;
 
+// Optional per-CTA timeline (compile with -DPUFF_TIMELINE): %globaltimer stamps at the phase
+// boundaries of the small-buffer kernels, read back with puff_advantage_sm100_timeline().
+// Compiled out of release builds.
+#ifdef PUFF_TIMELINE
+constexpr int kTimelineSlots = 12;
+constexpr int kTimelineCtas = 2048;
+__device__ unsigned long long g_timeline[kTimelineCtas * kTimelineSlots];
+#define PUFF_STAMP(slot)                                                                         \
+    do {                                                                                         \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x < kTimelineCtas) {                             \
+            unsigned long long t_;                                                               \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                               \
+            g_timeline[blockIdx.x * kTimelineSlots + (slot)] = t_;                               \
+        }                                                                                        \
+    } while (0)
+#else
+#define PUFF_STAMP(slot) do { } while (0)
+#endif
+
 constexpr int kTileRows = 32;              // segments per warp tile
 constexpr int kChunkCols = 32;             // columns per TMA box (128 bytes)
 constexpr int kBoxBytes = kTileRows * kChunkCols * 4;   // 4096
@@ -164,6 +183,22 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
 }
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may start while its predecessor in the stream is still running: its CTAs become
+// resident as soon as every CTA of the predecessor has executed launch_dependents (or exited) and
+// resources allow.  pdl_wait() then blocks until the predecessor grid has completed and its
+// memory operations are visible, so everything before it must touch no global memory that an
+// earlier kernel may still read or write: only the kernel's own set-up (shared-memory carve-up,
+// mbarrier initialisation, fetching the tensor-map descriptors, which are kernel parameters)
+// overlaps the predecessor's tail.  Both are no-ops in a launch without the attribute.
+__device__ __forceinline__ void pdl_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 __device__ __forceinline__ float4 lds128(uint32_t addr)
 {
     float4 v;
@@ -214,6 +249,62 @@ __device__ __forceinline__ uint32_t lds32u(uint32_t addr)
 __device__ __forceinline__ void sts32u(uint32_t addr, uint32_t v)
 {
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+// Shared-memory accesses of the chain loops.  No "memory" clobber: the compiler may move them
+// across ordinary arithmetic and across each other's neighbours, which is what lets the loads of
+// the next batch of steps issue under the dependent multiply-adds of the current one.  They stay
+// ordered among themselves and against every barrier, fence and mbarrier operation (all volatile
+// asm), and a store of A[t] can never pass the load of step t's operands: it needs their value.
+__device__ __forceinline__ float2 lds64_chain(uint32_t addr)
+{
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts32_chain(uint32_t addr, float v)
+{
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v));
+}
+
+// One row's recurrence A = delta + k*A over steps t = n_steps-1 .. 0 out of (delta, k) pairs in
+// shared memory: pair t at pairs + 8*t, A[t] stored to out + out_stride*t (out_stride 4: a dense
+// float row; 8 with out = pairs + 4: over the k of its own pair).  Batches of eight steps, the
+// next batch's pairs loaded before the current batch's dependent chain runs.
+__device__ __forceinline__ void chain_pairs_row(uint32_t pairs, uint32_t out, uint32_t out_stride, int n_steps,
+                                                float& a_run, float& abs_run)
+{
+    int t = n_steps - 1;
+    float2 cur[8];
+    if (t >= 7) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cur[j] = lds64_chain(pairs + 8u * static_cast<uint32_t>(t - j));
+    }
+    while (t >= 7) {
+        float2 nxt[8];
+        const bool more = t - 8 >= 7;
+        if (more) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) nxt[j] = lds64_chain(pairs + 8u * static_cast<uint32_t>(t - 8 - j));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            a_run = __fadd_rn(cur[j].x, __fmul_rn(cur[j].y, a_run));
+            sts32_chain(out + out_stride * static_cast<uint32_t>(t - j), a_run);
+            abs_run = __fadd_rn(abs_run, fabsf(a_run));
+        }
+        if (more) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+        }
+        t -= 8;
+    }
+    for (; t >= 0; --t) {
+        const float2 pr = lds64_chain(pairs + 8u * static_cast<uint32_t>(t));
+        a_run = __fadd_rn(pr.x, __fmul_rn(pr.y, a_run));
+        sts32_chain(out + out_stride * static_cast<uint32_t>(t), a_run);
+        abs_run = __fadd_rn(abs_run, fabsf(a_run));
+    }
 }
 
 // ---------------------------------------------------------------------------

@@ -37,6 +37,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                        float lambda, float rho_clip, float c_clip, long long num_segments,
                        int horizon, int tile_rows, long long num_tiles, int zero_last)
 {
+    if (threadIdx.x == 0) PUFF_STAMP(0);   // CTA start
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     float* const smem_f = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
@@ -55,6 +56,10 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
         fence_proxy_async();
     }
     __syncthreads();
+    if (tid == 0) PUFF_STAMP(1);   // set-up done
+    pdl_wait();   // nothing above reads or writes a tensor
+    pdl_launch_dependents();
+    if (tid == 0) PUFF_STAMP(2);   // predecessor complete
 
     const float gl = __fmul_rn(gamma, lambda);
     const float* const src[4] = {values, rewards, dones, importance};
@@ -88,10 +93,12 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                 if (!mbar_wait_thread(bar, parity)) failed = true;
                 parity ^= 1u;
             }
+            if (tid == 0 && tile == blockIdx.x) PUFF_STAMP(3);   // first tile: thread 0 saw the data
             if (__syncthreads_or(failed)) {
                 failed = true;
                 break;
             }
+            if (tid == 0 && tile == blockIdx.x) PUFF_STAMP(4);   // ... and so did everybody
         }
         // ---- 2. terms ----
         // a thread owns units of four consecutive elements (one 16-byte unit per array);
@@ -142,6 +149,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
             }
         }
         __syncthreads();   // every raw operand of the tile has been read
+        if (tid == 0 && tile == blockIdx.x) PUFF_STAMP(5);   // terms in registers
         float2* const st = reinterpret_cast<float2*>(sd);   // (delta, k) pairs over the d | w region
 #pragma unroll
         for (int u = 0; u < kB1MaxUnits; ++u) {
@@ -153,6 +161,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
             }
         }
         const bool any_nonbin = __syncthreads_or((nonbin << 1) != 0u || !(gain <= kPackedMaxGain));
+        if (tid == 0 && tile == blockIdx.x) PUFF_STAMP(6);   // pairs in shared memory
         // ---- 3. chain ----
         if (tid < 32) {
             const int lane = tid;
@@ -162,6 +171,10 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
             bool literal = any_nonbin;
             if (!literal) {
                 if (mine) {
+                    // plain accesses: the pairs (float2) and the advantages (float) are different
+                    // types, so the compiler is free to hoist the next steps' loads over the stores
+                    // and schedules the whole unrolled batch itself (measured faster here than the
+                    // explicit prefetch of chain_pairs_row)
                     int t = horizon - 2;
                     for (; t >= 7; t -= 8) {   // eight steps' operands first, then the dependent part
                         float2 p8[8];
@@ -201,6 +214,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
             if (mine && seg_abs_sum != nullptr) seg_abs_sum[tile * tile_rows + lane] = abs_run;
         }
         __syncthreads();
+        if (tid == 0 && tile == blockIdx.x) PUFF_STAMP(7);   // chain done
         // ---- 4. copy-out (advantages are in the v region), column H-1 of every row skipped ----
         {
             float* const g = advantages + goff;
@@ -232,8 +246,10 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
         // the stage is refilled by the async proxy next
         fence_proxy_async();
         __syncthreads();
+        if (tid == 0 && tile == blockIdx.x) PUFF_STAMP(8);   // first tile written out
     }
     if (failed && tid == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
+    if (tid == 0) PUFF_STAMP(10);
 }
 
 // ---------------------------------------------------------------------------
@@ -302,6 +318,8 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
         fence_proxy_async();
     }
     __syncthreads();
+    pdl_wait();   // nothing above reads or writes a tensor
+    pdl_launch_dependents();
 
     const float gl = __fmul_rn(gamma, lambda);
     bool failed = false;
@@ -465,26 +483,8 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
             float a_run = 0.0f, abs_run = 0.0f;
             bool literal = flag != 0u;
             if (!literal) {
-                if (mine) {
-                    int t = horizon - 2;
-                    for (; t >= 7; t -= 8) {   // eight steps' operands first, then the dependent part
-                        float2 p8[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) p8[j] = tp[ro + t - j];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            a_run = __fadd_rn(p8[j].x, __fmul_rn(p8[j].y, a_run));
-                            tp[ro + t - j].y = a_run;
-                            abs_run = __fadd_rn(abs_run, fabsf(a_run));
-                        }
-                    }
-                    for (; t >= 0; --t) {
-                        const float2 pr = tp[ro + t];
-                        a_run = __fadd_rn(pr.x, __fmul_rn(pr.y, a_run));
-                        tp[ro + t].y = a_run;
-                        abs_run = __fadd_rn(abs_run, fabsf(a_run));
-                    }
-                }
+                if (mine)   // in place: A[t] over the k of its own pair
+                    chain_pairs_row(smem_u32(tp + ro), smem_u32(tp + ro) + 4u, 8u, horizon - 1, a_run, abs_run);
                 literal = __any_sync(0xffffffffu, !(abs_run <= kPackedMaxAdv));   // the sum bounds every |A| of the row
             }
             if (literal) {   // rare: the reference's literal order, operands straight from global memory

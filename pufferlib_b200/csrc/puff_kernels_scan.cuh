@@ -33,6 +33,8 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
     const float gl = __fmul_rn(gamma, lambda);
     const int units = (horizon + 3) >> 2;          // units of 4 columns per row
     const int passes = (units + nt - 1) / nt;
+    pdl_wait();
+    pdl_launch_dependents();
 
     for (long long row = blockIdx.x; row < num_segments; row += gridDim.x) {
         const long long ro = row * horizon;
@@ -220,6 +222,8 @@ puff_adv_generic_kernel(const float* __restrict__ values, const float* __restric
                         long long horizon, int zero_last)
 {
     const float gl = __fmul_rn(gamma, lambda);
+    pdl_wait();
+    pdl_launch_dependents();
     for (long long row = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
          row < num_segments; row += static_cast<long long>(gridDim.x) * blockDim.x) {
         const long long ro = row * horizon;

@@ -32,6 +32,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
                       const float* adv_in, float* __restrict__ seg_abs_sum, float gamma, float lambda,
                       float rho_clip, float c_clip, long long num_segments, int horizon, int num_tiles)
 {
+    PUFF_STAMP(0);   // CTA start
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t out_base = base + NST * kStageBytes;
@@ -48,12 +49,22 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
         for (int s = 0; s < NST; ++s) mbar_init(bar_base + 8 * s, 1);
         fence_mbar_init();
         fence_proxy_async();
+        prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_r);
+        prefetch_tensormap(&tm_d);
+        prefetch_tensormap(&tm_w);
+        prefetch_tensormap(&tm_a);
     }
     __syncwarp();
+    PUFF_STAMP(1);   // set-up done
+    pdl_wait();   // nothing above reads or writes a tensor
+    PUFF_STAMP(2);   // predecessor complete
 
     // work item -> (tile k of this CTA, chunk c); chunks of a tile run from the last column
     // block down.  The issuing lane keeps its own running (k, c, stage) of the next item to
     // load, so that nothing but the TMA instructions stands between launch and first bytes.
+    // (Spreading the four boxes of an item over four lanes was measured and is slower: the
+    // divergent bookkeeping costs more than the serial issue of ~50 ns per box.)
     int ld_k = 0, ld_c = nchunks - 1, ld_s = 0, ld_i = 0;
     auto issue_next = [&]() {
         const int tile = static_cast<int>(blockIdx.x) + ld_k * static_cast<int>(gridDim.x);
@@ -77,8 +88,9 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
     if (lane == 0) {
         const int pre = total < NST ? total : NST;
         for (int i = 0; i < pre; ++i) issue_next();
-        prefetch_tensormap(&tm_a);
     }
+    pdl_launch_dependents();
+    PUFF_STAMP(3);   // first loads issued
 
     const float gl = __fmul_rn(gamma, lambda);
     const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
@@ -114,6 +126,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
             failed = true;
             break;
         }
+        if (i < 2) PUFF_STAMP(4 + 3 * i);   // data of item i arrived
         const uint32_t st = base + s * kStageBytes;
         const uint32_t ob = out_base + (i & 1) * kBoxBytes;
         const int cbase = c * kChunkCols;
@@ -149,6 +162,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
         }
         // generic-proxy reads of the stage and writes of the output box are
         // ordered before the async-proxy operations issued below
+        if (i < 2) PUFF_STAMP(5 + 3 * i);   // item i computed
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
@@ -156,6 +170,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
             bulk_commit();
             if (ld_i < total) issue_next();
         }
+        if (i < 2) PUFF_STAMP(6 + 3 * i);   // item i's store issued
         if (--c < 0) {
             c = nchunks - 1;
             ++k;
@@ -171,6 +186,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
         bulk_wait_read<0>();
         if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
     }
+    PUFF_STAMP(10);   // stores have left shared memory
 }
 
 
@@ -232,6 +248,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
     const uint32_t flag_base = bar_tfree + 8 * NT;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if (warp == 0) PUFF_STAMP(0);
 
     const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                          static_cast<int>(gridDim.x);
@@ -250,8 +267,16 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
         }
         fence_mbar_init();
         fence_proxy_async();
+        prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_r);
+        prefetch_tensormap(&tm_d);
+        prefetch_tensormap(&tm_w);
     }
+    if (warp == 0) PUFF_STAMP(1);
     __syncthreads();
+    pdl_wait();   // nothing above reads or writes a tensor
+    pdl_launch_dependents();
+    if (warp == 0) PUFF_STAMP(2);
 
     const float gl = __fmul_rn(gamma, lambda);
     bool failed = false;
@@ -259,10 +284,6 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
-            prefetch_tensormap(&tm_v);
-            prefetch_tensormap(&tm_r);
-            prefetch_tensormap(&tm_d);
-            prefetch_tensormap(&tm_w);
             // Loads are issued in groups of `group` consecutive chunks (NST % group == 0):
             // the producer waits until all their stages are free and then issues them back
             // to back, so that DRAM sees group*128 contiguous bytes of every row at once.
@@ -297,6 +318,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                         ++round;
                     }
                 }
+                if (i == 0) PUFF_STAMP(3);   // first group of loads issued
             }
             if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
         }
@@ -328,6 +350,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 failed = true;
                 break;
             }
+            if (warp == 2 && i == 0) PUFF_STAMP(4);   // data of item 0 arrived
             const uint32_t st = base + s * kStageBytes;
             float v[9], r[9], d[9], w[8];
             {
@@ -413,6 +436,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 mbar_arrive(bar_tfull + 8 * b);
                 mbar_arrive(bar_sfree + 8 * s);
             }
+            if (warp == 2 && i == 0) PUFF_STAMP(5);   // terms of item 0 written
             if (--c < 0) c = nchunks - 1;
             if (++s == NST) {
                 s = 0;
@@ -461,6 +485,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 failed = true;
                 break;
             }
+            if (i < 2) PUFF_STAMP(6 + 2 * i);   // chain warp has item i's terms
             const uint32_t tb = term_base + b * kTermBytes;
             float dl[32], kk[32], out[32];
 #pragma unroll
@@ -538,6 +563,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 const long long row = static_cast<long long>(tile) * kTileRows + lane;
                 if (row < num_segments) seg_abs_sum[row] = abs_run;
             }
+            if (i < 2) PUFF_STAMP(7 + 2 * i);   // item i chained and written to its output box
             pend = true;
             pend_x = cbase;
             pend_y = tile * kTileRows;
@@ -566,6 +592,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             bulk_wait_read<0>();
             if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
         }
+        PUFF_STAMP(10);   // stores have left shared memory
     }
 }
 
