@@ -35,6 +35,7 @@ extern "C" {
 #define PUFF_ERR_DEVICE_WAIT   -8   /* a bounded in-kernel wait gave up (see _device_status) */
 #define PUFF_ERR_WORKSPACE     -9   /* scratch / workspace too small or missing   */
 #define PUFF_ERR_SIZE         -10   /* size beyond what the entry point supports  */
+#define PUFF_ERR_DEVICE_BOUNDS -11  /* debug builds (PUFF_DEBUG_BOUNDS): a kernel formed an out-of-range index (see _device_status) */
 
 /* ---- kernel variants ----------------------------------------------------- */
 #define PUFF_VARIANT_AUTO       0   /* pick from (num_segments, horizon, alignment): a bit-exact serial kernel,

@@ -17,7 +17,8 @@ import subprocess
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libpuff_oracle.so")
+# PUFF_ORACLE_LIB names another build of the oracle (a sanitizer build) to load instead
+_LIB_PATH = os.environ.get("PUFF_ORACLE_LIB") or os.path.join(_HERE, "libpuff_oracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libpufferlib_ref.so")
 _REF_CUDA_PATH = os.path.join(_HERE, "_ref", "libpufferlib_ref_cuda.so")
 _lib = None

@@ -72,6 +72,16 @@ def _run(cmd, verbose):
     subprocess.run(cmd, check=True)
 
 
+def build_debug_cabi(out_path, verbose=False):
+    """The kernel library with -DPUFF_DEBUG_BOUNDS: every global-memory index
+    the kernels form is checked, a bad one sets PUFF_ERR_DEVICE_BOUNDS in the
+    status word and its access is skipped (nothing traps).  Slower; for tests
+    and debugging.  Written to `out_path`, never over the release library."""
+    sources = [os.path.join(CSRC, s) for s in CU_SOURCES]
+    _run([NVCC] + NVCC_FLAGS + ["-DPUFF_DEBUG_BOUNDS", "-o", out_path] + sources, verbose)
+    return out_path
+
+
 def build_cabi(force=False, verbose=False, ptxas_info=False):
     sources = [os.path.join(CSRC, s) for s in CU_SOURCES]
     headers = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cuh")]
@@ -111,4 +121,7 @@ def build_all(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    build_all(force="--force" in sys.argv, verbose=True)
+    if "--debug-bounds" in sys.argv:
+        build_debug_cabi(os.path.join(HERE, "libpuff_advantage_sm100_debug.so"), verbose=True)
+    else:
+        build_all(force="--force" in sys.argv, verbose=True)

@@ -11,12 +11,13 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libpuff_advantage_sm100.so")
+# PUFF_ADV_LIB names another build of the same library (a sanitizer or debug build) to load instead
+LIB_PATH = os.environ.get("PUFF_ADV_LIB") or os.path.join(_HERE, "libpuff_advantage_sm100.so")
 
 # error codes / variants / kernels of include/puff_advantage.h
 OK = 0
 ERR_NULL, ERR_SHAPE, ERR_VARIANT, ERR_ALIGN, ERR_ALIAS = -1, -2, -3, -4, -5
-ERR_ARCH, ERR_DRIVER, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_SIZE = -6, -7, -8, -9, -10
+ERR_ARCH, ERR_DRIVER, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_SIZE, ERR_DEVICE_BOUNDS = -6, -7, -8, -9, -10, -11
 NOALLOC_MAX_SEGMENTS = 524288
 EXCHANGE_HANDLE_BYTES = 64
 FLAG_ZERO_LAST_COLUMN = 1

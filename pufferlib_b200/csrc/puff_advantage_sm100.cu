@@ -592,6 +592,7 @@ extern "C" const char* puff_advantage_sm100_strerror(int code)
         case PUFF_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel gave up";
         case PUFF_ERR_WORKSPACE: return "scratch or workspace missing, misaligned or too small";
         case PUFF_ERR_SIZE: return "size beyond what this entry point supports";
+        case PUFF_ERR_DEVICE_BOUNDS: return "a kernel formed an out-of-range index (debug build)";
         default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
@@ -667,3 +668,20 @@ extern "C" int puff_advantage_sm100_set_tuning(int knob, int value)
 }
 
 extern "C" const char* puff_advantage_sm100_version(void) { return "0.1"; }
+
+#ifdef PUFF_DEBUG_BOUNDS
+// Debug builds only: proves that the index checks are compiled in and report.  One thread asks for
+// element `index` of an array of `extent` floats; an index outside it is recorded in the status
+// word and the access is skipped.
+namespace puff {
+__global__ void puff_bounds_selftest_kernel(float* buf, long long index, long long extent)
+{
+    stg_chk(buf, index, extent, 1.0f);
+}
+}  // namespace puff
+extern "C" int puff_advantage_sm100_bounds_selftest(float* device_buf, long long index, long long extent)
+{
+    puff_bounds_selftest_kernel<<<1, 1>>>(device_buf, index, extent);
+    return static_cast<int>(cudaGetLastError());
+}
+#endif

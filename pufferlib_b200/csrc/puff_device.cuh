@@ -29,9 +29,69 @@ __device__ unsigned long long g_timeline[kTimelineCtas * kTimelineSlots];
             g_timeline[blockIdx.x * kTimelineSlots + (slot)] = t_;                               \
         }                                                                                        \
     } while (0)
+// cycle accounting of a warp's loop phases: PUFF_TICK(acc) adds the cycles since the previous
+// tick to acc; PUFF_PUT(slot, acc) stores a total
+#define PUFF_TICK_DECL long long tick_prev_ = clock64()
+#define PUFF_TICK(acc)                          \
+    do {                                        \
+        const long long now_ = clock64();       \
+        (acc) += now_ - tick_prev_;             \
+        tick_prev_ = now_;                      \
+    } while (0)
+#define PUFF_PUT(slot, acc)                                                                                       \
+    do {                                                                                                          \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x < kTimelineCtas)                                                \
+            g_timeline[blockIdx.x * kTimelineSlots + (slot)] = static_cast<unsigned long long>(acc);             \
+    } while (0)
 #else
 #define PUFF_STAMP(slot) do { } while (0)
+#define PUFF_TICK_DECL do { } while (0)
+#define PUFF_TICK(acc) do { } while (0)
+#define PUFF_PUT(slot, acc) do { } while (0)
 #endif
+
+// Index checks of debug builds (compile with -DPUFF_DEBUG_BOUNDS): every global-memory index a
+// kernel forms is compared with the extent of its array.  A bad index records
+// PUFF_ERR_DEVICE_BOUNDS in the status word and the access is skipped (loads yield 0); nothing
+// traps.  Release builds compile the checks out.
+#ifdef PUFF_DEBUG_BOUNDS
+__device__ __forceinline__ bool idx_ok(long long i, long long n)
+{
+    if (i >= 0 && i < n) return true;
+    atomicExch(&g_device_status, PUFF_ERR_DEVICE_BOUNDS);
+    return false;
+}
+#else
+__device__ __forceinline__ constexpr bool idx_ok(long long, long long) { return true; }
+#endif
+__device__ __forceinline__ float ldg_chk(const float* base, long long i, long long n)
+{
+    return idx_ok(i, n) ? __ldg(base + i) : 0.0f;
+}
+// plain (coherent) load: for memory the same kernel also writes
+__device__ __forceinline__ float ld_chk(const float* base, long long i, long long n)
+{
+    return idx_ok(i, n) ? base[i] : 0.0f;
+}
+__device__ __forceinline__ float4 ldg4_chk(const float* base, long long i, long long n)
+{
+    return (idx_ok(i, n) && idx_ok(i + 3, n)) ? __ldg(reinterpret_cast<const float4*>(base + i))
+                                              : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+}
+__device__ __forceinline__ void stg_chk(float* base, long long i, long long n, float v)
+{
+    if (idx_ok(i, n)) base[i] = v;
+}
+__device__ __forceinline__ void stg4_chk(float* base, long long i, long long n, float4 v)
+{
+    if (idx_ok(i, n) && idx_ok(i + 3, n)) *reinterpret_cast<float4*>(base + i) = v;
+}
+// a TMA box may hang over the tensor's edge (it is clipped or zero-filled there), but its
+// origin must lie inside [0, width) x [0, rows)
+__device__ __forceinline__ bool box_ok(int x, int y, int width, long long rows)
+{
+    return idx_ok(x, width) && idx_ok(y, rows);
+}
 
 constexpr int kTileRows = 32;              // segments per warp tile
 constexpr int kChunkCols = 32;             // columns per TMA box (128 bytes)

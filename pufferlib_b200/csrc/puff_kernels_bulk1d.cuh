@@ -72,6 +72,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
         const int n_el = rows * horizon;
         const uint32_t bytes = static_cast<uint32_t>(n_el) * 4u;
         const long long goff = tile * tile_elems;
+        const long long total_elems = num_segments * horizon;
         // ---- 1. fetch ----
         // bulk copies for the 16-byte multiple of the span (all of it, except in a last tile
         // whose row count makes the byte size ragged), plain loads for the up to three
@@ -80,14 +81,16 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
             const uint32_t bulk_bytes = bytes & ~15u;
             if (bulk_bytes != 0u) {
                 if (tid == 0) {
+                    // debug builds: a span that leaves the arrays is recorded, and the first rows are read instead
+                    const long long from = idx_ok(goff + n_el - 1, total_elems) ? goff : 0;
                     mbar_expect_tx(bar, 4u * bulk_bytes);
-                    for (int a = 0; a < 4; ++a) bulk_load_1d(base + a * arr_pitch, src[a] + goff, bulk_bytes, bar);
+                    for (int a = 0; a < 4; ++a) bulk_load_1d(base + a * arr_pitch, src[a] + from, bulk_bytes, bar);
                 }
             }
             const int first_tail = static_cast<int>(bulk_bytes >> 2);
             if (tid < 4 * (n_el - first_tail)) {   // at most 12 threads
                 const int a = tid / (n_el - first_tail), e = first_tail + tid % (n_el - first_tail);
-                (smem_f + (a * arr_pitch) / 4)[e] = __ldg(src[a] + goff + e);
+                (smem_f + (a * arr_pitch) / 4)[e] = ldg_chk(src[a], goff + e, total_elems);
             }
             if (bulk_bytes != 0u) {
                 if (!mbar_wait_thread(bar, parity)) failed = true;
@@ -203,35 +206,34 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                 if (mine) {
                     const long long gro = goff + ro;
                     for (int t = horizon - 2; t >= 0; --t) {
-                        a_run = adv_step(__ldg(values + gro + t), __ldg(importance + gro + t), __ldg(values + gro + t + 1),
-                                         __ldg(rewards + gro + t + 1), __ldg(dones + gro + t + 1), a_run, gamma, gl,
-                                         rho_clip, c_clip);
+                        a_run = adv_step(ldg_chk(values, gro + t, total_elems), ldg_chk(importance, gro + t, total_elems),
+                                         ldg_chk(values, gro + t + 1, total_elems), ldg_chk(rewards, gro + t + 1, total_elems),
+                                         ldg_chk(dones, gro + t + 1, total_elems), a_run, gamma, gl, rho_clip, c_clip);
                         sv[ro + t] = a_run;
                         abs_run = __fadd_rn(abs_run, fabsf(a_run));
                     }
                 }
             }
-            if (mine && seg_abs_sum != nullptr) seg_abs_sum[tile * tile_rows + lane] = abs_run;
+            if (mine && seg_abs_sum != nullptr) stg_chk(seg_abs_sum, tile * tile_rows + lane, num_segments, abs_run);
         }
         __syncthreads();
         if (tid == 0 && tile == blockIdx.x) PUFF_STAMP(7);   // chain done
         // ---- 4. copy-out (advantages are in the v region), column H-1 of every row skipped ----
         {
-            float* const g = advantages + goff;
             const int n4 = n_el >> 2;   // the tile starts on a 16-byte boundary
             int col = (4 * tid) % horizon;
             for (int e4 = tid; e4 < n4; e4 += kB1Threads) {
                 const int e = e4 << 2;
                 const float4 a4 = *reinterpret_cast<const float4*>(sv + e);
                 if (col + 4 < horizon) {
-                    *reinterpret_cast<float4*>(g + e) = a4;
+                    stg4_chk(advantages, goff + e, total_elems, a4);
                 } else {
                     const float av[4] = {a4.x, a4.y, a4.z, a4.w};
                     int cj = col;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        if (cj != horizon - 1) g[e + j] = av[j];
-                        else if (zero_last) g[e + j] = 0.0f;
+                        if (cj != horizon - 1) stg_chk(advantages, goff + e + j, total_elems, av[j]);
+                        else if (zero_last) stg_chk(advantages, goff + e + j, total_elems, 0.0f);
                         cj = cj + 1 == horizon ? 0 : cj + 1;
                     }
                 }
@@ -239,8 +241,8 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                 if (col >= horizon) col -= horizon;
             }
             for (int e = (n4 << 2) + tid; e < n_el; e += kB1Threads) {
-                if (e % horizon != horizon - 1) g[e] = sv[e];
-                else if (zero_last) g[e] = 0.0f;
+                if (e % horizon != horizon - 1) stg_chk(advantages, goff + e, total_elems, sv[e]);
+                else if (zero_last) stg_chk(advantages, goff + e, total_elems, 0.0f);
             }
         }
         // the stage is refilled by the async proxy next
@@ -322,6 +324,7 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
     pdl_launch_dependents();
 
     const float gl = __fmul_rn(gamma, lambda);
+    const long long total_elems = num_segments * horizon;
     bool failed = false;
     auto rows_of = [&](long long tile) {
         const long long rem = num_segments - tile * tile_rows;
@@ -346,12 +349,15 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                 float* const stage_f = reinterpret_cast<float*>(smem_al + s * stage_bytes);
                 // ragged floats first: the arrive below publishes them together with the bulk bytes
                 for (int e = static_cast<int>(bulk_bytes >> 2); e < n_el; ++e)
-                    for (int a = 0; a < 4; ++a) (stage_f + a * (arr_pitch / 4))[e] = __ldg(src[a] + goff + e);
+                    for (int a = 0; a < 4; ++a)
+                        (stage_f + a * (arr_pitch / 4))[e] = ldg_chk(src[a], goff + e, total_elems);
                 const uint32_t bar = bar_full + 8 * s;
                 if (bulk_bytes != 0u) {
+                    // debug builds: a span that leaves the arrays is recorded, and the first rows are read instead
+                    const long long from = idx_ok(goff + n_el - 1, total_elems) ? goff : 0;
                     mbar_expect_tx(bar, 4u * bulk_bytes);
                     for (int a = 0; a < 4; ++a)
-                        bulk_load_1d(base + s * stage_bytes + a * arr_pitch, src[a] + goff, bulk_bytes, bar);
+                        bulk_load_1d(base + s * stage_bytes + a * arr_pitch, src[a] + from, bulk_bytes, bar);
                 } else {
                     mbar_arrive(bar);
                 }
@@ -367,7 +373,7 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
             const long long tile = blockIdx.x + n * gridDim.x;
             const int n_el = rows_of(tile) * horizon;
             const float2* const tp = reinterpret_cast<const float2*>(smem_al + term_base + b * term_bytes);
-            float* const g = advantages + tile * tile_elems;
+            const long long goff = tile * tile_elems;
             // unit by unit, the same units this thread fills in the terms pass: a thread only
             // ever overwrites pairs whose advantages it has itself written out
             const int n_grp = (n_el + 3) >> 2;
@@ -378,14 +384,14 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                 const float4 p1 = *reinterpret_cast<const float4*>(tp + e + 2);
                 const float av[4] = {p0.y, p0.w, p1.y, p1.w};
                 if (col + 4 < horizon && e + 4 <= n_el) {
-                    *reinterpret_cast<float4*>(g + e) = make_float4(av[0], av[1], av[2], av[3]);
+                    stg4_chk(advantages, goff + e, total_elems, make_float4(av[0], av[1], av[2], av[3]));
                 } else {
                     int cj = col;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         if (e + j < n_el) {
-                            if (cj != horizon - 1) g[e + j] = av[j];
-                            else if (zero_last) g[e + j] = 0.0f;
+                            if (cj != horizon - 1) stg_chk(advantages, goff + e + j, total_elems, av[j]);
+                            else if (zero_last) stg_chk(advantages, goff + e + j, total_elems, 0.0f);
                         }
                         cj = cj + 1 == horizon ? 0 : cj + 1;
                     }
@@ -493,15 +499,15 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                 if (mine) {
                     const long long gro = tile * tile_elems + ro;
                     for (int t = horizon - 2; t >= 0; --t) {
-                        a_run = adv_step(__ldg(values + gro + t), __ldg(importance + gro + t), __ldg(values + gro + t + 1),
-                                         __ldg(rewards + gro + t + 1), __ldg(dones + gro + t + 1), a_run, gamma, gl,
-                                         rho_clip, c_clip);
+                        a_run = adv_step(ldg_chk(values, gro + t, total_elems), ldg_chk(importance, gro + t, total_elems),
+                                         ldg_chk(values, gro + t + 1, total_elems), ldg_chk(rewards, gro + t + 1, total_elems),
+                                         ldg_chk(dones, gro + t + 1, total_elems), a_run, gamma, gl, rho_clip, c_clip);
                         tp[ro + t].y = a_run;
                         abs_run = __fadd_rn(abs_run, fabsf(a_run));
                     }
                 }
             }
-            if (mine && seg_abs_sum != nullptr) seg_abs_sum[tile * tile_rows + lane] = abs_run;
+            if (mine && seg_abs_sum != nullptr) stg_chk(seg_abs_sum, tile * tile_rows + lane, num_segments, abs_run);
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_cdone + 8 * b);
         }

@@ -38,16 +38,12 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
 
     for (long long row = blockIdx.x; row < num_segments; row += gridDim.x) {
         const long long ro = row * horizon;
-        const float* const v = values + ro;
-        const float* const r = rewards + ro;
-        const float* const d = dones + ro;
-        const float* const w = importance + ro;
-        float* const a = advantages + ro;
+        const long long total_elems = num_segments * horizon;
         float a_pass = 0.0f;      // advantage entering this pass (from later columns)
         float abs_acc = 0.0f;     // thread 0 only
         float gain = 0.0f;        // largest |(gamma*lambda)*c| of this thread's steps
         float chk = 0.0f;         // sum of this thread's |A|: inf or NaN as soon as one of them is
-        if (zero_last && tid == 0) a[horizon - 1] = 0.0f;
+        if (zero_last && tid == 0) stg_chk(advantages, ro + horizon - 1, total_elems, 0.0f);
 
         for (int p = 0; p < passes; ++p) {
             const int j = p * nt + tid;
@@ -65,10 +61,10 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
             for (int i = 0; i < 4; ++i) ww[i] = 0.0f;
             if (live) {
                 if (VEC) {   // horizon % 4 == 0 and 16-byte aligned bases
-                    const float4 v4 = __ldg(reinterpret_cast<const float4*>(v + col0));
-                    const float4 r4 = __ldg(reinterpret_cast<const float4*>(r + col0));
-                    const float4 d4 = __ldg(reinterpret_cast<const float4*>(d + col0));
-                    const float4 w4 = __ldg(reinterpret_cast<const float4*>(w + col0));
+                    const float4 v4 = ldg4_chk(values, ro + col0, total_elems);
+                    const float4 r4 = ldg4_chk(rewards, ro + col0, total_elems);
+                    const float4 d4 = ldg4_chk(dones, ro + col0, total_elems);
+                    const float4 w4 = ldg4_chk(importance, ro + col0, total_elems);
                     vv[0] = v4.x; vv[1] = v4.y; vv[2] = v4.z; vv[3] = v4.w;
                     rr[0] = r4.x; rr[1] = r4.y; rr[2] = r4.z; rr[3] = r4.w;
                     dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
@@ -77,17 +73,17 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         if (col0 + i < horizon) {
-                            vv[i] = __ldg(v + col0 + i);
-                            rr[i] = __ldg(r + col0 + i);
-                            dd[i] = __ldg(d + col0 + i);
-                            ww[i] = __ldg(w + col0 + i);
+                            vv[i] = ldg_chk(values, ro + col0 + i, total_elems);
+                            rr[i] = ldg_chk(rewards, ro + col0 + i, total_elems);
+                            dd[i] = ldg_chk(dones, ro + col0 + i, total_elems);
+                            ww[i] = ldg_chk(importance, ro + col0 + i, total_elems);
                         }
                     }
                 }
                 if (col0 + 4 < horizon) {
-                    vv[4] = __ldg(v + col0 + 4);
-                    rr[4] = __ldg(r + col0 + 4);
-                    dd[4] = __ldg(d + col0 + 4);
+                    vv[4] = ldg_chk(values, ro + col0 + 4, total_elems);
+                    rr[4] = ldg_chk(rewards, ro + col0 + 4, total_elems);
+                    dd[4] = ldg_chk(dones, ro + col0 + 4, total_elems);
                 }
             }
             // local composition over the (up to) four steps, latest column first
@@ -172,11 +168,11 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
             }
             if (live) {
                 if (VEC && col0 + 4 < horizon) {
-                    *reinterpret_cast<float4*>(a + col0) = make_float4(out[0], out[1], out[2], out[3]);
+                    stg4_chk(advantages, ro + col0, total_elems, make_float4(out[0], out[1], out[2], out[3]));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        if (col0 + i + 1 < horizon) a[col0 + i] = out[i];
+                        if (col0 + i + 1 < horizon) stg_chk(advantages, ro + col0 + i, total_elems, out[i]);
                 }
             }
             if (seg_abs_sum != nullptr) {
@@ -199,15 +195,16 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
             if (tid == 0) {
                 float a_run = 0.0f, abs_run = 0.0f;
                 for (int t = horizon - 2; t >= 0; --t) {
-                    a_run = adv_step(__ldg(v + t), __ldg(w + t), __ldg(v + t + 1), __ldg(r + t + 1), __ldg(d + t + 1),
-                                     a_run, gamma, gl, rho_clip, c_clip);
+                    a_run = adv_step(ldg_chk(values, ro + t, total_elems), ldg_chk(importance, ro + t, total_elems),
+                                     ldg_chk(values, ro + t + 1, total_elems), ldg_chk(rewards, ro + t + 1, total_elems),
+                                     ldg_chk(dones, ro + t + 1, total_elems), a_run, gamma, gl, rho_clip, c_clip);
                     abs_run = __fadd_rn(abs_run, fabsf(a_run));
-                    a[t] = a_run;
+                    stg_chk(advantages, ro + t, total_elems, a_run);
                 }
                 abs_acc = abs_run;
             }
         }
-        if (seg_abs_sum != nullptr && tid == 0) seg_abs_sum[row] = abs_acc;
+        if (seg_abs_sum != nullptr && tid == 0) stg_chk(seg_abs_sum, row, num_segments, abs_acc);
     }
 }
 
@@ -228,17 +225,18 @@ puff_adv_generic_kernel(const float* __restrict__ values, const float* __restric
          row < num_segments; row += static_cast<long long>(gridDim.x) * blockDim.x) {
         const long long ro = row * horizon;
         float a_run = 0.0f, abs_run = 0.0f;
-        float v_n = __ldg(values + ro + horizon - 1);
+        const long long total_elems = num_segments * horizon;
+        float v_n = ldg_chk(values, ro + horizon - 1, total_elems);
         for (long long t = horizon - 2; t >= 0; --t) {
-            const float v_t = __ldg(values + ro + t);
-            a_run = adv_step(v_t, __ldg(importance + ro + t), v_n, __ldg(rewards + ro + t + 1),
-                             __ldg(dones + ro + t + 1), a_run, gamma, gl, rho_clip, c_clip);
+            const float v_t = ldg_chk(values, ro + t, total_elems);
+            a_run = adv_step(v_t, ldg_chk(importance, ro + t, total_elems), v_n, ldg_chk(rewards, ro + t + 1, total_elems),
+                             ldg_chk(dones, ro + t + 1, total_elems), a_run, gamma, gl, rho_clip, c_clip);
             abs_run = __fadd_rn(abs_run, fabsf(a_run));
-            advantages[ro + t] = a_run;
+            stg_chk(advantages, ro + t, total_elems, a_run);
             v_n = v_t;
         }
-        if (zero_last) advantages[ro + horizon - 1] = 0.0f;
-        if (seg_abs_sum != nullptr) seg_abs_sum[row] = abs_run;
+        if (zero_last) stg_chk(advantages, ro + horizon - 1, total_elems, 0.0f);
+        if (seg_abs_sum != nullptr) stg_chk(seg_abs_sum, row, num_segments, abs_run);
     }
 }
 

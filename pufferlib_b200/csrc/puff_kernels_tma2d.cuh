@@ -70,8 +70,9 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
         const int tile = static_cast<int>(blockIdx.x) + ld_k * static_cast<int>(gridDim.x);
         const uint32_t st = base + ld_s * kStageBytes;
         const uint32_t bar = bar_base + 8 * ld_s;
-        const int x = ld_c * kChunkCols;
-        const int y = tile * kTileRows;
+        int x = ld_c * kChunkCols;
+        int y = tile * kTileRows;
+        if (!box_ok(x, y, horizon, num_segments)) x = y = 0;   // debug builds: recorded, and a valid box is read instead
         mbar_expect_tx(bar, kStageBytes);
         tma_load_2d(st + 0 * kBoxBytes, &tm_v, x, y, bar);
         tma_load_2d(st + 1 * kBoxBytes, &tm_r, x, y, bar);
@@ -102,7 +103,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
     float keep_next = 0.0f;                  // the same for the next tile, fetched one tile ahead
     if (adv_in != nullptr && my_tiles > 0) {
         const long long row = static_cast<long long>(blockIdx.x) * kTileRows + lane;
-        if (row < num_segments) keep_next = adv_in[row * horizon + horizon - 1];
+        if (row < num_segments) keep_next = ld_chk(adv_in, row * horizon + horizon - 1, num_segments * horizon);
     }
     int k = 0, c = nchunks - 1, s = 0;
     uint32_t parity = 0;
@@ -114,7 +115,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
             keep_next = 0.0f;
             if (adv_in != nullptr && k + 1 < my_tiles) {
                 const long long row = (static_cast<long long>(blockIdx.x) + static_cast<long long>(k + 1) * gridDim.x) * kTileRows + lane;
-                if (row < num_segments) keep_next = adv_in[row * horizon + horizon - 1];
+                if (row < num_segments) keep_next = ld_chk(adv_in, row * horizon + horizon - 1, num_segments * horizon);
             }
             a_run = 0.0f;
             abs_run = 0.0f;
@@ -158,7 +159,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
         const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
         if (EPI && c == 0) {
             const long long row = static_cast<long long>(tile) * kTileRows + lane;
-            if (row < num_segments) seg_abs_sum[row] = abs_run;
+            if (row < num_segments) stg_chk(seg_abs_sum, row, num_segments, abs_run);
         }
         // generic-proxy reads of the stage and writes of the output box are
         // ordered before the async-proxy operations issued below
@@ -166,7 +167,7 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-            tma_store_2d(&tm_a, cbase, tile * kTileRows, ob);
+            if (box_ok(cbase, tile * kTileRows, horizon, num_segments)) tma_store_2d(&tm_a, cbase, tile * kTileRows, ob);
             bulk_commit();
             if (ld_i < total) issue_next();
         }
@@ -303,7 +304,8 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                     const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
                     const uint32_t st = base + s * kStageBytes;
                     const uint32_t bar = bar_full + 8 * s;
-                    const int x = c * kChunkCols, y = tile * kTileRows;
+                    int x = c * kChunkCols, y = tile * kTileRows;
+                    if (!box_ok(x, y, horizon, num_segments)) x = y = 0;   // debug builds: recorded, a valid box is read instead
                     mbar_expect_tx(bar, kStageBytes);
                     tma_load_2d(st + 0 * kBoxBytes, &tm_v, x, y, bar);
                     tma_load_2d(st + 1 * kBoxBytes, &tm_r, x, y, bar);
@@ -318,7 +320,6 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                         ++round;
                     }
                 }
-                if (i == 0) PUFF_STAMP(3);   // first group of loads issued
             }
             if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
         }
@@ -336,6 +337,8 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
         float first_v = 0.0f, first_r = 0.0f, first_d = 0.0f;   // column 0 of the previous (later) chunk
         int c = nchunks - 1, s = 0, b = 0;
         uint32_t sround = 0, bround = 0;
+        [[maybe_unused]] long long cy_twait = 0, cy_twork = 0;
+        PUFF_TICK_DECL;
         for (int i = 0; i < total; ++i) {
             if (c == nchunks - 1) {   // tile start: nothing carries over
                 first_v = 0.0f;
@@ -350,7 +353,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 failed = true;
                 break;
             }
-            if (warp == 2 && i == 0) PUFF_STAMP(4);   // data of item 0 arrived
+            PUFF_TICK(cy_twait);
             const uint32_t st = base + s * kStageBytes;
             float v[9], r[9], d[9], w[8];
             {
@@ -436,7 +439,6 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 mbar_arrive(bar_tfull + 8 * b);
                 mbar_arrive(bar_sfree + 8 * s);
             }
-            if (warp == 2 && i == 0) PUFF_STAMP(5);   // terms of item 0 written
             if (--c < 0) c = nchunks - 1;
             if (++s == NST) {
                 s = 0;
@@ -446,6 +448,11 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 b = 0;
                 ++bround;
             }
+            PUFF_TICK(cy_twork);
+        }
+        if (warp == 2) {
+            PUFF_PUT(9, cy_twait);
+            PUFF_PUT(10, cy_twork);
         }
         if (failed && lane == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
     } else {
@@ -460,7 +467,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
         float keep_next = 0.0f;
         if (adv_in != nullptr && my_tiles > 0) {
             const long long row = static_cast<long long>(blockIdx.x) * kTileRows + lane;
-            if (row < num_segments) keep_next = adv_in[row * horizon + horizon - 1];
+            if (row < num_segments) keep_next = ld_chk(adv_in, row * horizon + horizon - 1, num_segments * horizon);
         }
         int k = 0, c = nchunks - 1, b = 0, oslot = 0;
         uint32_t bround = 0;
@@ -469,6 +476,8 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
         bool pend = false;
         int pend_x = 0, pend_y = 0;
         uint32_t pend_ob = 0;
+        [[maybe_unused]] long long cy_wait = 0, cy_load = 0, cy_chain = 0, cy_store = 0;
+        PUFF_TICK_DECL;
         for (int i = 0; i < total; ++i) {
             const int tile = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
             if (c == nchunks - 1) {   // tile start
@@ -476,7 +485,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 keep_next = 0.0f;
                 if (adv_in != nullptr && k + 1 < my_tiles) {
                     const long long row = (static_cast<long long>(tile) + gridDim.x) * kTileRows + lane;
-                    if (row < num_segments) keep_next = adv_in[row * horizon + horizon - 1];
+                    if (row < num_segments) keep_next = ld_chk(adv_in, row * horizon + horizon - 1, num_segments * horizon);
                 }
                 a_run = 0.0f;
                 abs_run = 0.0f;
@@ -485,7 +494,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 failed = true;
                 break;
             }
-            if (i < 2) PUFF_STAMP(6 + 2 * i);   // chain warp has item i's terms
+            PUFF_TICK(cy_wait);
             const uint32_t tb = term_base + b * kTermBytes;
             float dl[32], kk[32], out[32];
 #pragma unroll
@@ -502,7 +511,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             __syncwarp();
             if (lane == 0) {
                 if (pend) {
-                    tma_store_2d(&tm_a, pend_x, pend_y, pend_ob);
+                    if (box_ok(pend_x, pend_y, horizon, num_segments)) tma_store_2d(&tm_a, pend_x, pend_y, pend_ob);
                     bulk_commit();
                 }
                 if (flag != 0u) sts32u(flag_base + 4 * b, 0u);
@@ -510,6 +519,7 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 // with at most kWsOutSlots-1 stores still reading, this item's output box is free
                 bulk_wait_read<kWsOutSlots - 1>();
             }
+            PUFF_TICK(cy_load);
             const int cbase = c * kChunkCols;
             const float a_in = a_run;
             bool literal = flag != 0u;
@@ -535,18 +545,20 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 const long long row = static_cast<long long>(tile) * kTileRows + lane;
                 const bool in_rows = row < num_segments;
                 const long long ro = (in_rows ? row : 0) * horizon;
+                const long long total_elems = num_segments * horizon;
 #pragma unroll
                 for (int j = 31; j >= 0; --j) {
                     const int t = cbase + j;
                     if (in_rows && t < horizon - 1)
-                        a_run = adv_step(__ldg(raw_v + ro + t), __ldg(raw_w + ro + t), __ldg(raw_v + ro + t + 1),
-                                         __ldg(raw_r + ro + t + 1), __ldg(raw_d + ro + t + 1), a_run, gamma, gl,
-                                         rho_clip, c_clip);
+                        a_run = adv_step(ldg_chk(raw_v, ro + t, total_elems), ldg_chk(raw_w, ro + t, total_elems),
+                                         ldg_chk(raw_v, ro + t + 1, total_elems), ldg_chk(raw_r, ro + t + 1, total_elems),
+                                         ldg_chk(raw_d, ro + t + 1, total_elems), a_run, gamma, gl, rho_clip, c_clip);
                     out[j] = a_run;
                 }
                 abs_chunk = abs_tree32(out);
             }
             if (EPI) abs_run = __fadd_rn(abs_run, abs_chunk);
+            PUFF_TICK(cy_chain);
             const uint32_t ob = out_base + oslot * kBoxBytes;
             __syncwarp();   // lane 0 has seen this item's output box free (above)
             if (cbase + kChunkCols >= horizon) {   // the chunk that holds column H-1: it goes back unchanged
@@ -561,9 +573,8 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             }
             if (EPI && c == 0) {
                 const long long row = static_cast<long long>(tile) * kTileRows + lane;
-                if (row < num_segments) seg_abs_sum[row] = abs_run;
+                if (row < num_segments) stg_chk(seg_abs_sum, row, num_segments, abs_run);
             }
-            if (i < 2) PUFF_STAMP(7 + 2 * i);   // item i chained and written to its output box
             pend = true;
             pend_x = cbase;
             pend_y = tile * kTileRows;
@@ -577,12 +588,18 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
                 ++bround;
             }
             if (++oslot == kWsOutSlots) oslot = 0;
+            PUFF_TICK(cy_store);
         }
+        PUFF_PUT(4, cy_wait);
+        PUFF_PUT(5, cy_load);
+        PUFF_PUT(6, cy_chain);
+        PUFF_PUT(7, cy_store);
+        PUFF_PUT(8, total);
         if (pend && !failed) {   // the last item's store
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-                tma_store_2d(&tm_a, pend_x, pend_y, pend_ob);
+                if (box_ok(pend_x, pend_y, horizon, num_segments)) tma_store_2d(&tm_a, pend_x, pend_y, pend_ob);
                 bulk_commit();
             }
         }
@@ -592,7 +609,6 @@ puff_adv_tma2d_ws_kernel(const __grid_constant__ CUtensorMap tm_v,
             bulk_wait_read<0>();
             if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
         }
-        PUFF_STAMP(10);   // stores have left shared memory
     }
 }
 
