@@ -1,0 +1,134 @@
+"""Phase timeline of the advantage kernels on a GPU (a tracing aid, not a benchmark).
+
+    python -m pufferlib_b200.timeline cfg1            # small-buffer kernels: per-CTA phase stamps
+    python -m pufferlib_b200.timeline cfg2            # warp-specialised kernel: where its warps' cycles go
+    python -m pufferlib_b200.timeline cfg4
+
+Builds the kernel library with -DPUFF_TIMELINE into a scratch folder (the
+release library is not touched), runs the workload's kernel back to back from a
+CUDA graph, and reads the stamps back through puff_advantage_sm100_timeline:
+
+* single-warp tma2d / one-stage bulk1d kernels: %globaltimer at the phase
+  boundaries of every CTA's first tile (nanoseconds, relative to the earliest
+  CTA start of the last launch), shown as min / median / max over the CTAs;
+* warp-specialised tma2d kernel: clock64 totals of the chain warp's and one
+  terms warp's loop phases, per work item (a 32 x 32 chunk).
+
+The instrumented kernels run a few percent slower than the release build.
+"""
+import ctypes
+import os
+import sys
+import tempfile
+
+import numpy as np
+import torch
+
+from . import build, cabi
+from .workloads import WORKLOADS, Workload, make_inputs
+
+SLOTS = 12
+EXTRA = {"drive": Workload("drive", 8192, 91, gamma=0.98, lam=0.95, seed=7),
+         "odd_large": Workload("odd_large", 131072, 127, seed=8)}
+
+PHASES = {
+    "tma2d": ["CTA start", "set-up done", "predecessor complete (pdl_wait)", "first loads issued",
+              "item 0: data arrived", "item 0: computed", "item 0: store issued",
+              "item 1: data arrived", "item 1: computed", "item 1: store issued", "stores left shared memory"],
+    "bulk1d": ["CTA start", "set-up done", "predecessor complete (pdl_wait)", "tile 0: thread 0 has the data",
+               "tile 0: every thread has the data", "tile 0: terms in registers", "tile 0: (delta, k) pairs in shared memory",
+               "tile 0: chain done", "tile 0: written out", None, "CTA end"],
+}
+
+
+def build_timeline_library(folder):
+    path = os.path.join(folder, "libpuff_advantage_sm100_timeline.so")
+    sources = [os.path.join(build.CSRC, s) for s in build.CU_SOURCES]
+    build._run([build.NVCC] + build.NVCC_FLAGS + ["-DPUFF_TIMELINE", "-o", path] + sources, False)
+    lib = ctypes.CDLL(path)
+    for name, (res, args) in cabi.SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    lib.puff_advantage_sm100_timeline.restype = ctypes.c_int
+    lib.puff_advantage_sm100_timeline.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    return lib
+
+
+def run(name, launches=50):
+    wl = WORKLOADS.get(name) or EXTRA[name]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    S, H = wl.segments, wl.horizon
+    with tempfile.TemporaryDirectory() as folder:
+        lib = build_timeline_library(folder)
+        set_bytes = 20 * S * H
+        n_sets = 1 if set_bytes >= 252 << 20 else -(-(252 << 20) // set_bytes)
+        first = [t.to(dev) for t in make_inputs(wl)]
+        sets = [first + [torch.zeros((S, H), device=dev), torch.empty(S, device=dev)]]
+        for _ in range(n_sets - 1):
+            sets.append([t.clone() for t in first] + [torch.zeros((S, H), device=dev), torch.empty(S, device=dev)])
+        stream = torch.cuda.Stream()
+        variant = cabi.VARIANTS[wl.variant]
+
+        def launch(i):
+            v, r, d, w, adv, sums = sets[i % n_sets]
+            rc = lib.puff_advantage_sm100_launch(v.data_ptr(), r.data_ptr(), d.data_ptr(), w.data_ptr(), adv.data_ptr(),
+                                                 sums.data_ptr(), *wl.hyper(), S, H, variant,
+                                                 torch.cuda.current_stream().cuda_stream)
+            assert rc == 0, rc
+
+        n = max(n_sets, launches)
+        with torch.cuda.stream(stream):
+            for i in range(min(n, n_sets + 3)):
+                launch(i)
+        kernel = cabi.KERNEL_NAMES[lib.puff_advantage_sm100_last_kernel()]
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(n):
+                launch(i)
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        print(f"{wl.name}: {S} x {H}, kernel {kernel}, {1e3 * a.elapsed_time(b) / n:.2f} us per launch "
+              f"(instrumented build, {n} launches from one graph)")
+        ctas = 2048
+        buf = (ctypes.c_ulonglong * (SLOTS * ctas))()
+        assert lib.puff_advantage_sm100_timeline(buf, ctas) == 0
+        t = np.array(buf, dtype=np.int64).reshape(ctas, SLOTS)
+        t = t[t[:, 0] != 0]
+        # slot 8 holds an item count in the warp-specialised kernel and a %globaltimer stamp otherwise
+        ws = kernel == "tma2d" and len(t) > 0 and 0 < np.median(t[:, 8]) < 1e9
+        if ws:
+            t = t[t[:, 8] > 0]
+            items = t[:, 8].astype(np.float64)
+            print(f"warp-specialised kernel, {len(t)} CTAs, {np.median(items):.0f} work items (32 x 32 chunks) per CTA; "
+                  "cycles per item, median over CTAs:")
+            for slot, what in ((4, "chain warp: waiting for terms"), (5, "chain warp: loading terms, issuing the previous store"),
+                               (6, "chain warp: the recurrence"), (7, "chain warp: writing the output box"),
+                               (9, "terms warp: waiting (data, free buffer)"), (10, "terms warp: working")):
+                print(f"  {what:55s} {np.median(t[:, slot] / items):8.1f}")
+            return
+        names = PHASES.get(kernel)
+        if names is None:
+            print("no timeline stamps in this kernel")
+            return
+        t = t[t[:, 10] > 0]
+        if len(t) == 0:
+            print("this kernel form carries no timeline stamps")
+            return
+        t0 = t[:, 0].min()
+        print(f"{len(t)} CTAs stamped; ns after the earliest CTA start (min / median / max over CTAs):")
+        for i, nm in enumerate(names):
+            if nm is None:
+                continue
+            col = t[:, i][t[:, i] > 0] - t0
+            if len(col):
+                print(f"  {nm:45s} {col.min():7d} {int(np.median(col)):7d} {col.max():7d}")
+
+
+if __name__ == "__main__":
+    run(sys.argv[1] if len(sys.argv) > 1 else "cfg1")
