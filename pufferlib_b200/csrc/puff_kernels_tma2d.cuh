@@ -63,8 +63,8 @@ puff_adv_tma2d_kernel(const __grid_constant__ CUtensorMap tm_v,
     // work item -> (tile k of this CTA, chunk c); chunks of a tile run from the last column
     // block down.  The issuing lane keeps its own running (k, c, stage) of the next item to
     // load, so that nothing but the TMA instructions stands between launch and first bytes.
-    // (Spreading the four boxes of an item over four lanes was measured and is slower: the
-    // divergent bookkeeping costs more than the serial issue of ~50 ns per box.)
+    // (Spreading the boxes of an item over four lanes, or the first ring-full of items over as
+    // many lanes, was measured: slower and no faster respectively.)
     int ld_k = 0, ld_c = nchunks - 1, ld_s = 0, ld_i = 0;
     auto issue_next = [&]() {
         const int tile = static_cast<int>(blockIdx.x) + ld_k * static_cast<int>(gridDim.x);
