@@ -187,7 +187,9 @@ int puff_priorities_sm100_probs(const float* weights, const double* total_w,
  *             pointers from puff_exchange_sm100_mailbox(), indexed by rank
  *             (peer access between the devices must be enabled by the caller).
  *   _set_wait_ns  the bound of the in-kernel wait (default 2 s).
- *   _destroy  synchronises the device and frees everything.
+ *   _destroy  synchronises the device and frees everything.  Call it only after
+ *             every rank has finished its last exchange (a host-side barrier):
+ *             a peer whose kernel still stores into a freed mailbox would fault.
  *
  *   puff_priorities_sm100_weights_push   weights[s] as puff_priorities_sm100_weights,
  *             then the local fp64 total is stored into every rank's mailbox
