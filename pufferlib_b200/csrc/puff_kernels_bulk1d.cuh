@@ -335,13 +335,17 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
             const float* const src[4] = {values, rewards, dones, importance};
+            [[maybe_unused]] long long cy_pwait = 0, cy_pwork = 0;
+            PUFF_TICK_DECL;
             for (long long n = 0; n < my_tiles; ++n) {
                 const int s = static_cast<int>(n % kB1wStages);
                 const uint32_t round = static_cast<uint32_t>(n / kB1wStages);
+                PUFF_TICK(cy_pwork);
                 if (round > 0 && !mbar_wait_thread(bar_sfree + 8 * s, (round - 1) & 1u)) {
                     failed = true;
                     break;
                 }
+                PUFF_TICK(cy_pwait);
                 const long long tile = blockIdx.x + n * gridDim.x;
                 const int n_el = rows_of(tile) * horizon;
                 const long long goff = tile * tile_elems;
@@ -362,6 +366,8 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                     mbar_arrive(bar);
                 }
             }
+            PUFF_PUT(0, cy_pwait);
+            PUFF_PUT(1, my_tiles);
             if (failed) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
         }
     } else if (warp > kB1wTerms) {
@@ -400,12 +406,16 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                 if (col >= horizon) col -= horizon;
             }
         };
+        [[maybe_unused]] long long cy_tfullwait = 0, cy_terms = 0, cy_cwait = 0, cy_copy = 0;
+        PUFF_TICK_DECL;
         for (long long n = 0; n < my_tiles; ++n) {
             const int s = static_cast<int>(n % kB1wStages), b = static_cast<int>(n % kB1wTerms);
+            PUFF_TICK(cy_copy);
             if (!mbar_wait_warp(bar_full + 8 * s, static_cast<uint32_t>(n / kB1wStages) & 1u)) {
                 failed = true;
                 break;
             }
+            PUFF_TICK(cy_tfullwait);
             const long long tile = blockIdx.x + n * gridDim.x;
             const int n_el = rows_of(tile) * horizon;
             const int n_grp = (n_el + 3) >> 2;
@@ -452,6 +462,7 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                 mbar_arrive(bar_tfull + 8 * b);
                 mbar_arrive(bar_sfree + 8 * s);
             }
+            PUFF_TICK(cy_terms);
             // the previous tile has been chained meanwhile: write it out
             if (n > 0) {
                 const int pb = static_cast<int>((n - 1) % kB1wTerms);
@@ -459,8 +470,15 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                     failed = true;
                     break;
                 }
+                PUFF_TICK(cy_cwait);
                 copy_out(n - 1);
             }
+        }
+        if (warp == kB1wTerms + 1) {
+            PUFF_PUT(2, cy_tfullwait);
+            PUFF_PUT(3, cy_terms);
+            PUFF_PUT(4, cy_cwait);
+            PUFF_PUT(5, cy_copy);
         }
         if (!failed && my_tiles > 0) {
             const long long n = my_tiles - 1;
@@ -472,12 +490,16 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
         if (failed && lane == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
     } else {
         // ------------------------------- chain --------------------------------
+        [[maybe_unused]] long long cy_chwait = 0, cy_chwork = 0;
+        PUFF_TICK_DECL;
         for (long long n = warp - 1; n < my_tiles; n += kB1wTerms) {
             const int b = warp - 1;
+            PUFF_TICK(cy_chwork);
             if (!mbar_wait_warp(bar_tfull + 8 * b, static_cast<uint32_t>(n / kB1wTerms) & 1u)) {
                 failed = true;
                 break;
             }
+            PUFF_TICK(cy_chwait);
             const long long tile = blockIdx.x + n * gridDim.x;
             const int rows = rows_of(tile);
             float2* const tp = reinterpret_cast<float2*>(smem_al + term_base + b * term_bytes);
@@ -510,6 +532,11 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
             if (mine && seg_abs_sum != nullptr) stg_chk(seg_abs_sum, tile * tile_rows + lane, num_segments, abs_run);
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_cdone + 8 * b);
+        }
+        PUFF_TICK(cy_chwork);
+        if (warp == 1) {
+            PUFF_PUT(6, cy_chwait);
+            PUFF_PUT(7, cy_chwork);
         }
         if (failed && lane == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
     }

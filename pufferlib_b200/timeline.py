@@ -3,6 +3,7 @@
     python -m pufferlib_b200.timeline cfg1            # small-buffer kernels: per-CTA phase stamps
     python -m pufferlib_b200.timeline cfg2            # warp-specialised kernel: where its warps' cycles go
     python -m pufferlib_b200.timeline cfg4
+    python -m pufferlib_b200.timeline odd_large       # warp-specialised bulk1d kernel, 131072 x 127
 
 Builds the kernel library with -DPUFF_TIMELINE into a scratch folder (the
 release library is not touched), runs the workload's kernel back to back from a
@@ -11,8 +12,9 @@ CUDA graph, and reads the stamps back through puff_advantage_sm100_timeline:
 * single-warp tma2d / one-stage bulk1d kernels: %globaltimer at the phase
   boundaries of every CTA's first tile (nanoseconds, relative to the earliest
   CTA start of the last launch), shown as min / median / max over the CTAs;
-* warp-specialised tma2d kernel: clock64 totals of the chain warp's and one
-  terms warp's loop phases, per work item (a 32 x 32 chunk).
+* warp-specialised kernels: clock64 totals of the loop phases of the chain warp,
+  one terms warp (and, for bulk1d, the producer), per work item (a 32 x 32
+  chunk for tma2d, a tile for bulk1d).
 
 The instrumented kernels run a few percent slower than the release build.
 """
@@ -111,6 +113,17 @@ def run(name, launches=50):
                                (6, "chain warp: the recurrence"), (7, "chain warp: writing the output box"),
                                (9, "terms warp: waiting (data, free buffer)"), (10, "terms warp: working")):
                 print(f"  {what:55s} {np.median(t[:, slot] / items):8.1f}")
+            return
+        if kernel == "bulk1d" and len(t) > 0 and 0 < np.median(t[:, 1]) < 1e9 and t[:, 10].max() == 0:
+            # warp-specialised bulk1d: slot 1 holds a tile count, the rest clock64 totals
+            tiles = t[:, 1].astype(np.float64)
+            print(f"warp-specialised bulk1d kernel, {len(t)} CTAs, {np.median(tiles):.0f} tiles per CTA; "
+                  "cycles per tile, median over CTAs (a chain warp takes every other tile):")
+            for slot, what in ((0, "producer: waiting for a free stage"), (2, "terms warp: waiting for data"),
+                               (3, "terms warp: computing terms"), (4, "terms warp: waiting for the previous tile's chain"),
+                               (5, "terms warp: writing the previous tile out"), (6, "chain warp 0: waiting for terms"),
+                               (7, "chain warp 0: chaining")):
+                print(f"  {what:55s} {np.median(t[:, slot] / tiles):8.1f}")
             return
         names = PHASES.get(kernel)
         if names is None:
