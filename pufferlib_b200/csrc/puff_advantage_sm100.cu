@@ -322,8 +322,8 @@ static int bulk1d_tile_rows(long long horizon, int max_smem, size_t* smem_bytes)
     return 0;
 }
 
-// Warp-specialised bulk1d: two raw stages and two terms buffers, 48 bytes of shared memory
-// per element of a tile; the largest of 32/16/8/4 rows that fits, 0 if none does
+// Warp-specialised bulk1d: two raw stages, two terms buffers and two output tiles, 56 bytes of
+// shared memory per element of a tile; the largest of 32/16/8/4 rows that fits, 0 if none does
 static int bulk1d_ws_tile_rows(long long horizon, int max_smem, size_t* smem_bytes)
 {
     const int cand[4] = {32, 16, 8, 4};
@@ -331,7 +331,7 @@ static int bulk1d_ws_tile_rows(long long horizon, int max_smem, size_t* smem_byt
     for (int i = 0; i < 4; ++i) {
         if (cand[i] > cap && cand[i] > 4) continue;
         const size_t arr = (static_cast<size_t>(cand[i]) * horizon * 4 + 15) & ~static_cast<size_t>(15);
-        const size_t need = (kB1wStages * 4 + kB1wTerms * 2) * arr + 8 * (2 * kB1wStages + 2 * kB1wTerms) + 4 * kB1wTerms + 64 + 128;
+        const size_t need = (kB1wStages * 4 + kB1wTerms * 3) * arr + 8 * (2 * kB1wStages + 2 * kB1wTerms) + 4 * kB1wTerms + 64 + 128;
         if (need > static_cast<size_t>(max_smem)) continue;
         *smem_bytes = need;
         return cand[i];

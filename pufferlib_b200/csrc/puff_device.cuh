@@ -230,6 +230,11 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
+__device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit()
 {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");

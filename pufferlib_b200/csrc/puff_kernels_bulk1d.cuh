@@ -25,7 +25,12 @@ namespace puff {
 //      A = delta + k*A, A written into the v region (stride H words: conflict-free
 //      for odd H).  A non-binary nn or advantages near the overflow range send the
 //      tile down the reference's literal order, operands straight from global memory
-//   4. copy-out, all threads: coalesced 128-bit stores that skip column H-1
+//   4. write-out: the finished tile is dense in the v region and contiguous in global memory,
+//      so it leaves through ONE 1-D bulk store issued by thread 0 (a memory system that is busy
+//      reading takes plain stores slowly: the 128-bit stores this replaces took 1 us per tile).
+//      The store covers column H-1 as well: lane r reads its row's advantages[H-1] while the
+//      tile's inputs are in flight and the store writes that value back (0 when the op owns
+//      the column)
 constexpr int kB1Threads = 128;
 constexpr int kB1MaxUnits = 9;                                   // units of four elements per thread
 constexpr int kB1MaxElems = kB1Threads * kB1MaxUnits * 4;         // elements per tile (72 KB of stage)
@@ -73,6 +78,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
         const uint32_t bytes = static_cast<uint32_t>(n_el) * 4u;
         const long long goff = tile * tile_elems;
         const long long total_elems = num_segments * horizon;
+        float keep_last = 0.0f;   // warp 0, lane = row
         // ---- 1. fetch ----
         // bulk copies for the 16-byte multiple of the span (all of it, except in a last tile
         // whose row count makes the byte size ragged), plain loads for the up to three
@@ -83,11 +89,16 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                 if (tid == 0) {
                     // debug builds: a span that leaves the arrays is recorded, and the first rows are read instead
                     const long long from = idx_ok(goff + n_el - 1, total_elems) ? goff : 0;
+                    bulk_wait_read<0>();   // the previous tile's store has read the v region
                     mbar_expect_tx(bar, 4u * bulk_bytes);
                     for (int a = 0; a < 4; ++a) bulk_load_1d(base + a * arr_pitch, src[a] + from, bulk_bytes, bar);
                 }
             }
+            // the caller's advantages[row, H-1], for the write-out (requested now, used after the chain)
+            if (tid < rows && !zero_last) keep_last = ld_chk(advantages, goff + static_cast<long long>(tid) * horizon + horizon - 1, total_elems);
             const int first_tail = static_cast<int>(bulk_bytes >> 2);
+            if (bulk_bytes == 0u && tid == 0) bulk_wait_read<0>();
+            if (bulk_bytes == 0u) __syncthreads();   // (a tile of one to three floats: plain loads only)
             if (tid < 4 * (n_el - first_tail)) {   // at most 12 threads
                 const int a = tid / (n_el - first_tail), e = first_tail + tid % (n_el - first_tail);
                 (smem_f + (a * arr_pitch) / 4)[e] = ldg_chk(src[a], goff + e, total_elems);
@@ -215,41 +226,25 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                 }
             }
             if (mine && seg_abs_sum != nullptr) stg_chk(seg_abs_sum, tile * tile_rows + lane, num_segments, abs_run);
-        }
-        __syncthreads();
-        if (tid == 0 && tile == blockIdx.x) PUFF_STAMP(7);   // chain done
-        // ---- 4. copy-out (advantages are in the v region), column H-1 of every row skipped ----
-        {
-            const int n4 = n_el >> 2;   // the tile starts on a 16-byte boundary
-            int col = (4 * tid) % horizon;
-            for (int e4 = tid; e4 < n4; e4 += kB1Threads) {
-                const int e = e4 << 2;
-                const float4 a4 = *reinterpret_cast<const float4*>(sv + e);
-                if (col + 4 < horizon) {
-                    stg4_chk(advantages, goff + e, total_elems, a4);
-                } else {
-                    const float av[4] = {a4.x, a4.y, a4.z, a4.w};
-                    int cj = col;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (cj != horizon - 1) stg_chk(advantages, goff + e + j, total_elems, av[j]);
-                        else if (zero_last) stg_chk(advantages, goff + e + j, total_elems, 0.0f);
-                        cj = cj + 1 == horizon ? 0 : cj + 1;
-                    }
-                }
-                col += grp_stride_cols;
-                if (col >= horizon) col -= horizon;
+            // ---- 4. write-out ----
+            if (mine) sv[ro + horizon - 1] = keep_last;
+            fence_proxy_async();
+            __syncwarp();
+            const uint32_t out_bytes = bytes & ~15u;
+            if (lane == 0) {
+                if (out_bytes != 0u && idx_ok(goff + n_el - 1, total_elems))
+                    bulk_store_1d(advantages + goff, smem_u32(sv), out_bytes);
+                bulk_commit();
             }
-            for (int e = (n4 << 2) + tid; e < n_el; e += kB1Threads) {
-                if (e % horizon != horizon - 1) stg_chk(advantages, goff + e, total_elems, sv[e]);
-                else if (zero_last) stg_chk(advantages, goff + e, total_elems, 0.0f);
-            }
+            for (int e = static_cast<int>(out_bytes >> 2) + lane; e < n_el; e += 32)   // ragged last tile
+                stg_chk(advantages, goff + e, total_elems, sv[e]);
         }
-        // the stage is refilled by the async proxy next
+        // every generic access to the stage is ordered before the async-proxy refill of the next tile
         fence_proxy_async();
         __syncthreads();
-        if (tid == 0 && tile == blockIdx.x) PUFF_STAMP(8);   // first tile written out
+        if (tid == 0 && tile == blockIdx.x) PUFF_STAMP(7);   // chain done, store issued
     }
+    if (tid == 0) bulk_wait_read<0>();   // the last store has left shared memory
     if (failed && tid == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
     if (tid == 0) PUFF_STAMP(10);
 }
@@ -262,12 +257,17 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
 //   warp 0       producer: four cp.async.bulk copies per tile into a 2-deep ring of raw
 //                stages (plus plain loads of the up to three ragged floats per array)
 //   warps 3..10  terms: stream over the flat tile in units of four elements and write
-//                (delta, k) pairs into one of two terms buffers; afterwards they copy the
-//                finished advantages of the previous tile out to global memory with
-//                coalesced 128-bit stores that skip column H-1
-//   warps 1, 2   chain: warp b owns terms buffer b (every other tile); lane r walks row r
-//                in place, A = delta + k*A stored over k; literal order from global memory
-//                when a non-binary nn was flagged or the advantages near the overflow range
+//                (delta, k) pairs into one of two terms buffers
+//   warps 1, 2   chain: warp b owns terms buffer b and output buffer b (every other tile);
+//                lane r walks row r, A = delta + k*A, into a dense [rows][H] output tile that
+//                leaves through ONE 1-D bulk store (a whole tile is contiguous in global
+//                memory).  The store covers column H-1 as well, so the lane first reads its
+//                row's advantages[H-1] and the store writes that value back (or 0 when the
+//                op owns the column).  Literal order from global memory when a non-binary nn
+//                was flagged or the advantages near the overflow range.
+// (Cycle accounting of an earlier form, in which the terms warps wrote the tiles out with plain
+// 128-bit stores, showed them spending as long in those stores as in the terms: a memory system
+// that is busy reading takes plain stores slowly, and the raw stages were held up behind them.)
 // One CTA per SM; tiles are pipelined inside it, so the kernel streams at buffer sizes
 // where the one-stage bulk1d kernel is still phase-bound.
 constexpr int kB1wStages = 2;
@@ -298,7 +298,8 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
     const uint32_t stage_bytes = 4u * arr_pitch;
     const uint32_t term_bytes = 2u * arr_pitch;                                          // (delta, k) pairs
     const uint32_t term_base = kB1wStages * stage_bytes;
-    const uint32_t bar_off = term_base + kB1wTerms * term_bytes;
+    const uint32_t out_base = term_base + kB1wTerms * term_bytes;                        // dense advantages, per chain warp
+    const uint32_t bar_off = out_base + kB1wTerms * arr_pitch;
     const uint32_t bar_full = base + bar_off;
     const uint32_t bar_sfree = bar_full + 8 * kB1wStages;
     const uint32_t bar_tfull = bar_sfree + 8 * kB1wStages;
@@ -374,38 +375,6 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
         // --------------------------- terms + copy-out --------------------------
         const int tt = (warp - 1 - kB1wTerms) * 32 + lane;   // 0 .. kB1wTermThreads-1
         const int unit_stride_cols = (4 * kB1wTermThreads) % horizon;
-        auto copy_out = [&](long long n) {       // advantages of tile n sit in the .y of its pairs
-            const int b = static_cast<int>(n % kB1wTerms);
-            const long long tile = blockIdx.x + n * gridDim.x;
-            const int n_el = rows_of(tile) * horizon;
-            const float2* const tp = reinterpret_cast<const float2*>(smem_al + term_base + b * term_bytes);
-            const long long goff = tile * tile_elems;
-            // unit by unit, the same units this thread fills in the terms pass: a thread only
-            // ever overwrites pairs whose advantages it has itself written out
-            const int n_grp = (n_el + 3) >> 2;
-            int col = (4 * tt) % horizon;
-            for (int e4 = tt; e4 < n_grp; e4 += kB1wTermThreads) {
-                const int e = e4 << 2;
-                const float4 p0 = *reinterpret_cast<const float4*>(tp + e);
-                const float4 p1 = *reinterpret_cast<const float4*>(tp + e + 2);
-                const float av[4] = {p0.y, p0.w, p1.y, p1.w};
-                if (col + 4 < horizon && e + 4 <= n_el) {
-                    stg4_chk(advantages, goff + e, total_elems, make_float4(av[0], av[1], av[2], av[3]));
-                } else {
-                    int cj = col;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (e + j < n_el) {
-                            if (cj != horizon - 1) stg_chk(advantages, goff + e + j, total_elems, av[j]);
-                            else if (zero_last) stg_chk(advantages, goff + e + j, total_elems, 0.0f);
-                        }
-                        cj = cj + 1 == horizon ? 0 : cj + 1;
-                    }
-                }
-                col += unit_stride_cols;
-                if (col >= horizon) col -= horizon;
-            }
-        };
         [[maybe_unused]] long long cy_tfullwait = 0, cy_terms = 0, cy_cwait = 0, cy_copy = 0;
         PUFF_TICK_DECL;
         for (long long n = 0; n < my_tiles; ++n) {
@@ -416,6 +385,13 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                 break;
             }
             PUFF_TICK(cy_tfullwait);
+            // terms buffer b was last used by tile n - kB1wTerms: its chain must be through with it
+            if (n >= kB1wTerms &&
+                !mbar_wait_warp(bar_cdone + 8 * b, static_cast<uint32_t>(n / kB1wTerms - 1) & 1u)) {
+                failed = true;
+                break;
+            }
+            PUFF_TICK(cy_cwait);
             const long long tile = blockIdx.x + n * gridDim.x;
             const int n_el = rows_of(tile) * horizon;
             const int n_grp = (n_el + 3) >> 2;
@@ -463,29 +439,12 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                 mbar_arrive(bar_sfree + 8 * s);
             }
             PUFF_TICK(cy_terms);
-            // the previous tile has been chained meanwhile: write it out
-            if (n > 0) {
-                const int pb = static_cast<int>((n - 1) % kB1wTerms);
-                if (!mbar_wait_warp(bar_cdone + 8 * pb, static_cast<uint32_t>((n - 1) / kB1wTerms) & 1u)) {
-                    failed = true;
-                    break;
-                }
-                PUFF_TICK(cy_cwait);
-                copy_out(n - 1);
-            }
         }
         if (warp == kB1wTerms + 1) {
             PUFF_PUT(2, cy_tfullwait);
             PUFF_PUT(3, cy_terms);
             PUFF_PUT(4, cy_cwait);
             PUFF_PUT(5, cy_copy);
-        }
-        if (!failed && my_tiles > 0) {
-            const long long n = my_tiles - 1;
-            if (mbar_wait_warp(bar_cdone + 8 * static_cast<int>(n % kB1wTerms), static_cast<uint32_t>(n / kB1wTerms) & 1u))
-                copy_out(n);
-            else
-                failed = true;
         }
         if (failed && lane == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
     } else {
@@ -503,16 +462,24 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
             const long long tile = blockIdx.x + n * gridDim.x;
             const int rows = rows_of(tile);
             float2* const tp = reinterpret_cast<float2*>(smem_al + term_base + b * term_bytes);
+            float* const ob = reinterpret_cast<float*>(smem_al + out_base + b * arr_pitch);
             const uint32_t flag = lds32u(flag_base + 4 * b);
             __syncwarp();
-            if (lane == 0 && flag != 0u) sts32u(flag_base + 4 * b, 0u);
+            if (lane == 0) {
+                if (flag != 0u) sts32u(flag_base + 4 * b, 0u);
+                bulk_wait_read<0>();   // this warp's previous store has read the output buffer
+            }
             const int ro = lane * horizon;
             const bool mine = lane < rows;
+            const long long goff = tile * tile_elems;
+            // the caller's advantages[row, H-1] goes back unchanged (0 when the op owns the column)
+            float keep_last = 0.0f;
+            if (mine && !zero_last) keep_last = ld_chk(advantages, goff + ro + horizon - 1, total_elems);
+            __syncwarp();
             float a_run = 0.0f, abs_run = 0.0f;
             bool literal = flag != 0u;
             if (!literal) {
-                if (mine)   // in place: A[t] over the k of its own pair
-                    chain_pairs_row(smem_u32(tp + ro), smem_u32(tp + ro) + 4u, 8u, horizon - 1, a_run, abs_run);
+                if (mine) chain_pairs_row(smem_u32(tp + ro), smem_u32(ob + ro), 4u, horizon - 1, a_run, abs_run);
                 literal = __any_sync(0xffffffffu, !(abs_run <= kPackedMaxAdv));   // the sum bounds every |A| of the row
             }
             if (literal) {   // rare: the reference's literal order, operands straight from global memory
@@ -524,15 +491,29 @@ puff_adv_bulk1d_ws_kernel(const float* __restrict__ values, const float* __restr
                         a_run = adv_step(ldg_chk(values, gro + t, total_elems), ldg_chk(importance, gro + t, total_elems),
                                          ldg_chk(values, gro + t + 1, total_elems), ldg_chk(rewards, gro + t + 1, total_elems),
                                          ldg_chk(dones, gro + t + 1, total_elems), a_run, gamma, gl, rho_clip, c_clip);
-                        tp[ro + t].y = a_run;
+                        ob[ro + t] = a_run;
                         abs_run = __fadd_rn(abs_run, fabsf(a_run));
                     }
                 }
             }
+            if (mine) ob[ro + horizon - 1] = keep_last;
             if (mine && seg_abs_sum != nullptr) stg_chk(seg_abs_sum, tile * tile_rows + lane, num_segments, abs_run);
+            // the output tile is complete: one bulk store for its 16-byte multiple, plain stores for
+            // the up to three trailing floats of a ragged last tile
+            fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_cdone + 8 * b);
+            const int n_el = rows * horizon;
+            const uint32_t bulk_bytes = (static_cast<uint32_t>(n_el) * 4u) & ~15u;
+            if (lane == 0) {
+                mbar_arrive(bar_cdone + 8 * b);   // the pairs have been consumed
+                if (bulk_bytes != 0u && idx_ok(goff + n_el - 1, total_elems))
+                    bulk_store_1d(advantages + goff, smem_u32(ob), bulk_bytes);
+                bulk_commit();
+            }
+            for (int e = static_cast<int>(bulk_bytes >> 2) + lane; e < n_el; e += 32)
+                stg_chk(advantages, goff + e, total_elems, ob[e]);
         }
+        if (lane == 0) bulk_wait_read<0>();   // the last store has left shared memory
         PUFF_TICK(cy_chwork);
         if (warp == 1) {
             PUFF_PUT(6, cy_chwait);

@@ -39,7 +39,7 @@ PHASES = {
               "item 1: data arrived", "item 1: computed", "item 1: store issued", "stores left shared memory"],
     "bulk1d": ["CTA start", "set-up done", "predecessor complete (pdl_wait)", "tile 0: thread 0 has the data",
                "tile 0: every thread has the data", "tile 0: terms in registers", "tile 0: (delta, k) pairs in shared memory",
-               "tile 0: chain done", "tile 0: written out", None, "CTA end"],
+               "tile 0: chain done, bulk store issued", None, None, "CTA end"],
 }
 
 
@@ -120,9 +120,8 @@ def run(name, launches=50):
             print(f"warp-specialised bulk1d kernel, {len(t)} CTAs, {np.median(tiles):.0f} tiles per CTA; "
                   "cycles per tile, median over CTAs (a chain warp takes every other tile):")
             for slot, what in ((0, "producer: waiting for a free stage"), (2, "terms warp: waiting for data"),
-                               (3, "terms warp: computing terms"), (4, "terms warp: waiting for the previous tile's chain"),
-                               (5, "terms warp: writing the previous tile out"), (6, "chain warp 0: waiting for terms"),
-                               (7, "chain warp 0: chaining")):
+                               (4, "terms warp: waiting for a free terms buffer"), (3, "terms warp: computing terms"),
+                               (6, "chain warp 0: waiting for terms"), (7, "chain warp 0: chaining, storing")):
                 print(f"  {what:55s} {np.median(t[:, slot] / tiles):8.1f}")
             return
         names = PHASES.get(kernel)
