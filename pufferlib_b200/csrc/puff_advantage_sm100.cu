@@ -477,19 +477,15 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             }
             const long long tiles = (rows + kTileRows - 1) / kTileRows;
             float* abs_p = seg_abs_sum != nullptr ? seg_abs_sum + r0 : nullptr;
-            // Large buffers: the warp-specialised kernel.  Measured on 131072 x 256: four raw
-            // stages whose loads are issued two chunks at a time, two terms buffers, two CTAs
-            // per SM (more CTAs per SM lowered the achieved DRAM rate).  Buffers of only a few
-            // chunks per SM finish sooner on the single-warp kernel, whose pipeline has fewer
-            // hops, and rows of one or two chunks stay on it at any size (33.5 M elements,
-            // single-warp against warp-specialised: H = 32 128.7 us / 128.9, H = 64 112.4 / 112.4,
-            // H = 96 114.5 / 106.5, H = 128 110.3 / 103.9, H = 160 111.5 / 105.3; at 2-8 M
-            // elements the two are within a few percent from H = 96 on, and the single warp
-            // is 3-5 % ahead at H = 32).
+            // The warp-specialised kernel.  Measured on 131072 x 256: four raw stages whose loads
+            // are issued two chunks at a time, two terms buffers, two CTAs per SM (more CTAs per
+            // SM lowered the achieved DRAM rate).  With programmatic dependent launch hiding its
+            // longer set-up it is level with or ahead of the single-warp kernel at every size
+            // measured (single-warp / warp-specialised, us): 1024 x 64 3.34 / 3.34, 8192 x 64
+            // 4.73 / 4.67, 1024 x 256 8.92 / 6.65, 4096 x 256 9.65 / 7.78, 8192 x 128 7.73 / 6.64,
+            // 32768 x 64 11.98 / 10.48, 524288 x 64 115.7 / 110.9, 1048576 x 32 131.0 / 129.1.
             // PUFF_TUNE_WS_STAGES: 0 = single-warp, N = warp-specialised with N raw stages (2, 3, 4, 6).
-            const long long nchunks = (horizon + kChunkCols - 1) / kChunkCols;
-            const long long work_items = tiles * nchunks;
-            const int ws = tune(PUFF_TUNE_WS_STAGES, (work_items >= 8LL * dev->sm_count && nchunks >= 3) ? 4 : 0);
+            const int ws = tune(PUFF_TUNE_WS_STAGES, 4);
             if (ws != 0) {
                 const int wnst = ws <= 2 ? 2 : ws == 3 ? 3 : ws <= 5 ? 4 : 6;
                 const int smem = wnst * kStageBytes + 2 * kTermBytes + kWsOutSlots * kBoxBytes + 2048;
@@ -525,10 +521,11 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
         // PUFF_TUNE_WS_STAGES: 0 = one-stage kernel, otherwise the warp-specialised pipeline
         size_t ws_smem = 0;
         const int ws_rows = bulk1d_ws_tile_rows(horizon, dev->max_smem_optin, &ws_smem);
-        // measured at H = 127: the pipeline wins from a few thousand tiles on (131072 rows:
-        // 65 us against 72 us); at 10007 rows the one-stage kernel is ahead (10.6 against 12.5 us)
+        // measured at H = 127 (one-stage against pipeline): 10007 rows, two tiles per SM, 9.9 against
+        // 10.2 us; 20000 rows 17.7 / 13.8; 32768 rows 25.1 / 17.4; 131072 rows 67.2 / 54.9.  The
+        // pipeline takes over from three tiles per SM.
         const long long ws_tiles = ws_rows > 0 ? (num_segments + ws_rows - 1) / ws_rows : 0;
-        const int use_ws = ws_rows > 0 ? tune(PUFF_TUNE_WS_STAGES, ws_tiles >= 8LL * dev->sm_count ? 1 : 0) : 0;
+        const int use_ws = ws_rows > 0 ? tune(PUFF_TUNE_WS_STAGES, ws_tiles >= 3LL * dev->sm_count ? 1 : 0) : 0;
         if (use_ws != 0) {
             const long long tiles = (num_segments + ws_rows - 1) / ws_rows;
             const long long max_grid = persistent_sms(dev->sm_count);
