@@ -169,7 +169,7 @@ puff_prio_probs_gathered_kernel(const float* __restrict__ weights, const ExSlot*
     __shared__ double s_total;
     __shared__ int s_ok;
     if (threadIdx.x < 32) {
-        const unsigned long long seq = ctl->seq;    // the push of this round precedes this kernel in its stream
+        const unsigned long long seq = ctl->seq;    // the push of this exchange precedes this kernel in its stream
         const int lane = threadIdx.x;
         const ExSlot* slot = mailbox + (seq % kExRing) * world + (lane < world ? lane : 0);
         bool here = lane >= world || ld_acquire_sys_u64(&slot->seq) == seq;

@@ -80,7 +80,7 @@ def test_a_missing_peer_ends_the_wait_with_a_status_not_a_hang():
         a.set_wait_ns(5_000_000)      # 5 ms
         sums_a, sums_b = _sums(5000, 1), _sums(4000, 2)
         wa = a.weights_push(sums_a, ALPHA)
-        probs, total = a.probs_gathered(wa)          # rank 1 never pushed this round
+        probs, total = a.probs_gathered(wa)          # rank 1 never pushed its total
         torch.cuda.synchronize()
         assert cabi.device_status() == cabi.ERR_DEVICE_WAIT
         assert cabi.device_status() == 0             # cleared by the read; the context is intact
