@@ -33,6 +33,25 @@ class OracleKernels:
         return (weights + 1e-6) / (total.float() + 1e-6)
 
 
+class GatherExchange:
+    """Stand-in with the interface of exchange.PeerExchange for CPU ranks: every
+    rank's total reaches every rank (an all-gather over gloo stands where the
+    kernels store into peer mailboxes) and is added in rank order."""
+
+    def weights_push(self, seg_abs_sum, alpha):
+        w = torch.nan_to_num(seg_abs_sum ** alpha, 0, 0, 0)
+        mine = w.double().sum().reshape(1)
+        self._totals = [torch.zeros(1, dtype=torch.float64) for _ in range(dist.get_world_size())]
+        dist.all_gather(self._totals, mine)
+        return w
+
+    def probs_gathered(self, weights):
+        total = torch.zeros(1, dtype=torch.float64)
+        for t in self._totals:          # rank order on every rank
+            total = total + t
+        return (weights + 1e-6) / (total.float() + 1e-6), total
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -41,13 +60,14 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, wl, out_dir):
+def _worker(rank, world, port, wl, out_dir, use_exchange=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         full = make_inputs(wl)
-        sh = ShardedAdvantage(wl.segments, wl.horizon, wl.hyper(), ALPHA, kernels=OracleKernels())
+        sh = ShardedAdvantage(wl.segments, wl.horizon, wl.hyper(), ALPHA, kernels=OracleKernels(),
+                              exchange=GatherExchange() if use_exchange else None)
         assert (sh.lo, sh.hi) == shard_rows(wl.segments, rank, world)
         local = [t[sh.lo:sh.hi].contiguous() for t in full]
         adv = torch.zeros_like(local[0])
@@ -60,11 +80,17 @@ def _worker(rank, world, port, wl, out_dir):
         dist.destroy_process_group()
 
 
-def test_two_rank_sharded_step_matches_single_process(tmp_path):
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("use_exchange", [False, True])
+def test_two_rank_sharded_step_matches_single_process(tmp_path, use_exchange):
+    """Both ways the total can cross ranks: an all-reduce between the two
+    priority steps, or an exchange object whose two steps move it themselves."""
     from oracle import puff_oracle
     wl = Workload("shard", 1001, 48, seed=17, done_p=0.05)
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), wl, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), wl, str(tmp_path), use_exchange), nprocs=world, join=True)
 
     full = [t.numpy() for t in make_inputs(wl)]
     adv = np.zeros_like(full[0])
