@@ -297,6 +297,7 @@ class PathTimer:
         self.pending = collections.deque()
         self.last = {}
         self.windows = []
+        self.status_errors = []
 
     # -- one step in its three forms -------------------------------------------
     def step(self, i):
@@ -359,9 +360,7 @@ class PathTimer:
         t1.record()
         self.fence()
         self.windows.append((w0, time.time()))
-        status = cabi.device_status()
-        if status != 0:
-            raise SystemExit(f"bench.py: a kernel reported status {status} ({cabi.strerror(status)}) in the timed region")
+        self._check_status()
         return t0.elapsed_time(t1), per
 
     def timed_eager(self, fn, total_steps):
@@ -376,10 +375,17 @@ class PathTimer:
         t1.record()
         self.fence()
         self.windows.append((w0, time.time()))
+        self._check_status()
+        return t0.elapsed_time(t1), 1
+
+    def _check_status(self):
+        """A bounded wait that gave up inside a kernel invalidates the timed region.  It is
+        recorded and reported in the JSON line (`device_status`) rather than raised: one rank
+        leaving early would strand the others in their next collective."""
+        from pufferlib_b200 import cabi
         status = cabi.device_status()
         if status != 0:
-            raise SystemExit(f"bench.py: a kernel reported status {status} ({cabi.strerror(status)}) in the timed region")
-        return t0.elapsed_time(t1), 1
+            self.status_errors.append(f"{status}: {cabi.strerror(status)}")
 
 
 def max_over_ranks(values, dev, world):
@@ -510,6 +516,7 @@ def run_b200_arm(args, wl, rank, local_rank, world):
                   "what": "ms_per_step: exchange overlapped with the next step's kernel (as the headline); "
                           "kernel_plus_exchange_serial_us: kernel, weights, exchange, probabilities on one stream"}
         timer.windows += st.windows
+        timer.status_errors += st.status_errors
         del st, local
 
     # ---- small and odd workloads: steady-state kernel time (single GPU only) -------
@@ -581,6 +588,10 @@ def run_b200_arm(args, wl, rank, local_rank, world):
                "api": "puff_advantage_sm100_host (C ABI, pinned host buffers)"}
 
     clocks = sampler.stop(timer.windows) if sampler is not None else None
+    final_status = cabi.device_status()
+    if final_status != 0:
+        timer.status_errors.append(f"{final_status}: {cabi.strerror(final_status)}")
+    n_bad = max_over_ranks([len(timer.status_errors)], dev, world)[0]
 
     if rank == 0:
         peak, peak_kind = hbm_peak()
@@ -610,6 +621,8 @@ def run_b200_arm(args, wl, rank, local_rank, world):
             "e2e": e2e,
             "gpu_launches": launches,
             "clocks": clocks,
+            # 0 on every rank, or this run's numbers are void: a kernel gave up a bounded wait
+            "device_status": "ok" if n_bad == 0 else {"ranks_max_errors": int(n_bad), "rank0": timer.status_errors},
         }
         if strong is not None:
             line["strong_scaling"] = strong
