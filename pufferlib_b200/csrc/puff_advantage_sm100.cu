@@ -14,17 +14,17 @@
 //           segments, the horizon walked backwards in chunks of 32 columns; each
 //           chunk of the four inputs arrives as a 32x32 TMA box in 128B-swizzled
 //           shared memory behind an mbarrier ring, and the advantages leave through
-//           a TMA store.  Two forms: one warp per CTA doing everything (small
-//           buffers), and a warp-specialised CTA of a producer warp, four warps
-//           that compute what does not depend on the running advantage, and one
-//           warp that runs the recurrence (large buffers).  TMA clips a store at
+//           a TMA store.  Two forms: a warp-specialised CTA of a producer warp,
+//           four warps that compute what does not depend on the running advantage,
+//           and one warp that runs the recurrence (the default), and one warp per
+//           CTA doing everything (on request).  TMA clips a store at
 //           the tensor edge in whole 16-byte units only, so column H-1 cannot be
 //           masked out of the box: each lane reads its row's advantages[H-1] once
 //           per tile and the store writes that same value back.
 //   bulk1d  serial, bit-exact, for H % 4 != 0 (row pitch not a multiple of
 //           16 bytes, so no 2-D tensor map exists): tiles of 4..32 whole rows
-//           are contiguous spans, fetched with 1-D bulk copies.  One-stage and
-//           warp-specialised forms.
+//           are contiguous spans, fetched with 1-D bulk copies and written back
+//           with one 1-D bulk store per tile.  One-stage and warp-specialised forms.
 //   scan    T threads per row, 4 steps per thread: local affine composition,
 //           warp-shuffle + shared-memory scan of the (k, d) pairs, serial
 //           replay of the 4 steps from the scanned carry-in.  For long rows

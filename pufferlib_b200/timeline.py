@@ -1,8 +1,8 @@
 """Phase timeline of the advantage kernels on a GPU (a tracing aid, not a benchmark).
 
-    python -m pufferlib_b200.timeline cfg1            # small-buffer kernels: per-CTA phase stamps
-    python -m pufferlib_b200.timeline cfg2            # warp-specialised kernel: where its warps' cycles go
-    python -m pufferlib_b200.timeline cfg4
+    python -m pufferlib_b200.timeline cfg2            # warp-specialised tma2d kernel: where its warps' cycles go
+    python -m pufferlib_b200.timeline cfg4            # one-stage bulk1d kernel: per-CTA phase stamps
+    PUFF_ADV_WS=0 python -m pufferlib_b200.timeline cfg1   # single-warp tma2d kernel: per-CTA phase stamps
     python -m pufferlib_b200.timeline odd_large       # warp-specialised bulk1d kernel, 131072 x 127
 
 Builds the kernel library with -DPUFF_TIMELINE into a scratch folder (the
