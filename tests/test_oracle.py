@@ -116,3 +116,52 @@ def test_minibatch_oracle_matches_torch_sequence():
     np.testing.assert_allclose(o_n, e.numpy(), rtol=1e-12, atol=1e-14)
     np.testing.assert_allclose(o_r, (a64[idx] + v64[idx]).numpy(), rtol=0, atol=0)
     np.testing.assert_allclose(o_p, mb_prio.numpy()[:, 0], rtol=1e-13)
+
+
+def _numpy_restatement(v, r, d, w, gamma, lam, rho_clip, c_clip, sentinel):
+    """The recurrence of pufferlib.cpp:28-41 column by column over all rows at
+    once, every operation rounded to fp32 in the reference's order."""
+    f = np.float32
+    S, H = v.shape
+    adv = np.full((S, H), sentinel, dtype=np.float32)
+    a = np.zeros(S, dtype=np.float32)
+    gl = f(f(gamma) * f(lam))
+    with np.errstate(all="ignore"):
+        for t in range(H - 2, -1, -1):
+            nn = (1.0 - d[:, t + 1].astype(np.float64)).astype(np.float32)   # a double subtraction there
+            rho = np.minimum(w[:, t], f(rho_clip))
+            c = np.minimum(w[:, t], f(c_clip))
+            td = (r[:, t + 1] + (f(gamma) * v[:, t + 1]) * nn) - v[:, t]
+            delta = rho * td
+            a = delta + ((gl * c) * a) * nn
+            adv[:, t] = a
+    return adv
+
+
+def test_oracle_matches_a_vectorised_restatement_on_random_shapes():
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=40, deadline=None)
+    @given(S=st.integers(1, 40), H=st.integers(1, 70), seed=st.integers(0, 2 ** 16),
+           gamma=st.sampled_from([0.0, 0.9, 0.99, 1.0]), lam=st.sampled_from([0.0, 0.5, 0.95, 1.0]),
+           rho_clip=st.sampled_from([0.0, 0.5, 1.0, 3.0]), c_clip=st.sampled_from([0.0, 0.9, 1.0, 2.5]),
+           done_p=st.sampled_from([0.0, 0.05, 0.5, 1.0]))
+    def check(S, H, seed, gamma, lam, rho_clip, c_clip, done_p):
+        rng = np.random.default_rng(seed)
+        v = rng.standard_normal((S, H)).astype(np.float32)
+        r = rng.standard_normal((S, H)).astype(np.float32)
+        d = (rng.random((S, H)) < done_p).astype(np.float32)
+        w = np.exp(rng.standard_normal((S, H))).astype(np.float32)
+        hyper = (gamma, lam, rho_clip, c_clip)
+        got = oracle_advantage([v, r, d, w], hyper)
+        want = _numpy_restatement(v, r, d, w, *hyper, SENTINEL)
+        assert bits_equal(got, want), first_mismatch(got, want)
+        # rows are independent: any row block gives the same bits
+        if S > 1:
+            part = oracle_advantage([a[S // 2:] for a in (v, r, d, w)], hyper)
+            assert bits_equal(part, got[S // 2:])
+        # scaling values and rewards by a power of two scales the advantages exactly
+        scaled = oracle_advantage([v * 4, r * 4, d, w], hyper)
+        assert bits_equal(scaled[:, :-1], got[:, :-1] * 4)
+
+    check()
