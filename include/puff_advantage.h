@@ -337,7 +337,8 @@ int puff_advantage_sm100_inject_status(int value);
 #define PUFF_TUNE_RESERVE_SMS   6   /* PUFF_ADV_RESERVE_SMS: SMs the persistent (warp-specialised) grids leave free for other streams' kernels */
 #define PUFF_TUNE_TILE_ROWS     7   /* PUFF_ADV_TILE_ROWS: cap on the rows per tile of the bulk1d kernels (4, 8, 16, 32) */
 #define PUFF_TUNE_PDL           8   /* PUFF_ADV_PDL: 0 = launch without programmatic stream serialization */
-#define PUFF_TUNE_COUNT         9
+#define PUFF_TUNE_SCAN_WIDE     9   /* PUFF_ADV_SCAN_WIDE: 0 = the scan kernel always takes four columns per thread and pass */
+#define PUFF_TUNE_COUNT        10
 int puff_advantage_sm100_set_tuning(int knob, int value);
 /* Library version, "major.minor". */
 const char* puff_advantage_sm100_version(void);

@@ -223,7 +223,7 @@ static void tune_init()
         static const char* const names[PUFF_TUNE_COUNT] = {"PUFF_ADV_FORCE_KERNEL", "PUFF_ADV_STAGES", "PUFF_ADV_WS",
                                                            "PUFF_ADV_CTAS_PER_SM", "PUFF_ADV_GROUP",
                                                            "PUFF_ADV_SCAN_THREADS", "PUFF_ADV_RESERVE_SMS",
-                                                           "PUFF_ADV_TILE_ROWS", "PUFF_ADV_PDL"};
+                                                           "PUFF_ADV_TILE_ROWS", "PUFF_ADV_PDL", "PUFF_ADV_SCAN_WIDE"};
         for (int i = 0; i < PUFF_TUNE_COUNT; ++i) {
             const char* v = getenv(names[i]);
             g_tune[i].store((v != nullptr && *v != '\0') ? atoi(v) : -1, std::memory_order_relaxed);
@@ -545,23 +545,29 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
         }
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
     } else if (kernel == PUFF_KERNEL_SCAN) {
-        const long long units = (horizon + 3) / 4;
-        // 512 threads at most: with ~60 registers per thread two such CTAs share an SM,
-        // so 256 rows of 4096 columns run as one wave (measured 7.4 us against 9.1 us with 1024)
+        // Threads per row: a power of two up to 512 (with ~60 registers per thread two such CTAs
+        // share an SM, so 256 rows of 4096 columns run as one wave).  A thread takes four columns
+        // per pass, or eight when the row would otherwise need a second pass: half the scans and
+        // barriers, and all of a thread's loads in flight at once.
+        const long long units4 = (horizon + 3) / 4;
         int nt = 32;
-        while (nt < 512 && nt < units) nt <<= 1;
+        while (nt < 512 && nt < units4) nt <<= 1;
         {
             const int o = tune(PUFF_TUNE_SCAN_THREADS, 0);
             if (o >= 32 && o <= 1024 && (o & (o - 1)) == 0) nt = o;
         }
+        const bool wide = units4 > nt && nt <= 512 && tune(PUFF_TUNE_SCAN_WIDE, 1) != 0;
         const long long max_grid = static_cast<long long>(dev->sm_count) * (2048 / nt) ;
         const int grid = static_cast<int>(num_segments < max_grid ? num_segments : max_grid);
-        if (aligned16 && horizon % 4 == 0)
-            err = launch_kernel(puff_adv_scan_kernel<true>, grid, nt, 0, st, values, rewards, dones, importance, advantages,
-                                seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon), zero_last);
-        else
-            err = launch_kernel(puff_adv_scan_kernel<false>, grid, nt, 0, st, values, rewards, dones, importance, advantages,
-                                seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon), zero_last);
+        const bool vec = aligned16 && horizon % 4 == 0;
+#define PUFF_SCAN_CASE(V, U)                                                                                          \
+    err = launch_kernel(puff_adv_scan_kernel<V, U>, grid, nt, 0, st, values, rewards, dones, importance, advantages, \
+                        seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments, static_cast<int>(horizon), zero_last)
+        if (vec && wide) PUFF_SCAN_CASE(true, 2);
+        else if (vec) PUFF_SCAN_CASE(true, 1);
+        else if (wide) PUFF_SCAN_CASE(false, 2);
+        else PUFF_SCAN_CASE(false, 1);
+#undef PUFF_SCAN_CASE
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
     } else {
         const long long blocks = (num_segments + 127) / 128;

@@ -6,23 +6,26 @@
 namespace puff {
 
 // ---------------------------------------------------------------------------
-// scan: NT threads per row, 4 steps per thread, affine-pair scan of the carries
+// scan: NT threads per row, W = 4*UPT steps per thread, affine-pair scan of the carries
 // ---------------------------------------------------------------------------
 // A_t = delta_t + k_t * A_{t+1} with k_t = ((gamma*lambda)*c_t)*nn_t.  Thread j
-// of a pass owns the unit of four columns G-1-j counted from the end of the
+// of a pass owns the unit of W columns G-1-j counted from the end of the
 // row, so the suffix scan in time is an inclusive prefix scan over j.  The
-// composed pair (K, D) of a unit maps the advantage entering it (column 4g+4)
-// to the one leaving it (column 4g): A_out = D + K * A_in.  After the scan each
-// thread knows its own A_in and replays its four steps in the reference's
+// composed pair (K, D) of a unit maps the advantage entering it (column Wg+W)
+// to the one leaving it (column Wg): A_out = D + K * A_in.  After the scan each
+// thread knows its own A_in and replays its W steps in the reference's
 // operation order, so only the carry-in differs from the serial result.
-template <bool VEC>
-__global__ void __launch_bounds__(1024)
+// UPT = 2 halves the number of passes (and of scans and barriers) of a long row and puts
+// all of a thread's loads in flight at once.
+template <bool VEC, int UPT>
+__global__ void __launch_bounds__(1024 / UPT)
 puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
                      const float* __restrict__ dones, const float* __restrict__ importance,
                      float* __restrict__ advantages, float* __restrict__ seg_abs_sum, float gamma,
                      float lambda, float rho_clip, float c_clip, long long num_segments, int horizon,
                      int zero_last)
 {
+    constexpr int W = 4 * UPT;
     __shared__ float s_k[32], s_d[32], s_abs[32];
     __shared__ float s_carry;
     const int tid = threadIdx.x;
@@ -31,7 +34,7 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
     const int warp = tid >> 5;
     const int nwarps = nt >> 5;
     const float gl = __fmul_rn(gamma, lambda);
-    const int units = (horizon + 3) >> 2;          // units of 4 columns per row
+    const int units = (horizon + W - 1) / W;       // units of W columns per row
     const int passes = (units + nt - 1) / nt;
     pdl_wait();
     pdl_launch_dependents();
@@ -49,29 +52,34 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
             const int j = p * nt + tid;
             const int g = units - 1 - j;
             const bool live = g >= 0;
-            const int col0 = g << 2;
-            float vv[5], rr[5], dd[5], ww[4];   // index i <-> column col0+i
+            const int col0 = g * W;
+            float vv[W + 1], rr[W + 1], dd[W + 1], ww[W];   // index i <-> column col0+i
 #pragma unroll
-            for (int i = 0; i < 5; ++i) {
+            for (int i = 0; i < W + 1; ++i) {
                 vv[i] = 0.0f;
                 rr[i] = 0.0f;
                 dd[i] = 0.0f;
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) ww[i] = 0.0f;
+            for (int i = 0; i < W; ++i) ww[i] = 0.0f;
             if (live) {
                 if (VEC) {   // horizon % 4 == 0 and 16-byte aligned bases
-                    const float4 v4 = ldg4_chk(values, ro + col0, total_elems);
-                    const float4 r4 = ldg4_chk(rewards, ro + col0, total_elems);
-                    const float4 d4 = ldg4_chk(dones, ro + col0, total_elems);
-                    const float4 w4 = ldg4_chk(importance, ro + col0, total_elems);
-                    vv[0] = v4.x; vv[1] = v4.y; vv[2] = v4.z; vv[3] = v4.w;
-                    rr[0] = r4.x; rr[1] = r4.y; rr[2] = r4.z; rr[3] = r4.w;
-                    dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
-                    ww[0] = w4.x; ww[1] = w4.y; ww[2] = w4.z; ww[3] = w4.w;
+#pragma unroll
+                    for (int u = 0; u < UPT; ++u) {
+                        if (col0 + 4 * u < horizon) {   // the last unit of a row may be half empty
+                            const float4 v4 = ldg4_chk(values, ro + col0 + 4 * u, total_elems);
+                            const float4 r4 = ldg4_chk(rewards, ro + col0 + 4 * u, total_elems);
+                            const float4 d4 = ldg4_chk(dones, ro + col0 + 4 * u, total_elems);
+                            const float4 w4 = ldg4_chk(importance, ro + col0 + 4 * u, total_elems);
+                            vv[4 * u] = v4.x; vv[4 * u + 1] = v4.y; vv[4 * u + 2] = v4.z; vv[4 * u + 3] = v4.w;
+                            rr[4 * u] = r4.x; rr[4 * u + 1] = r4.y; rr[4 * u + 2] = r4.z; rr[4 * u + 3] = r4.w;
+                            dd[4 * u] = d4.x; dd[4 * u + 1] = d4.y; dd[4 * u + 2] = d4.z; dd[4 * u + 3] = d4.w;
+                            ww[4 * u] = w4.x; ww[4 * u + 1] = w4.y; ww[4 * u + 2] = w4.z; ww[4 * u + 3] = w4.w;
+                        }
+                    }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
+                    for (int i = 0; i < W; ++i) {
                         if (col0 + i < horizon) {
                             vv[i] = ldg_chk(values, ro + col0 + i, total_elems);
                             rr[i] = ldg_chk(rewards, ro + col0 + i, total_elems);
@@ -80,28 +88,27 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
                         }
                     }
                 }
-                if (col0 + 4 < horizon) {
-                    vv[4] = ldg_chk(values, ro + col0 + 4, total_elems);
-                    rr[4] = ldg_chk(rewards, ro + col0 + 4, total_elems);
-                    dd[4] = ldg_chk(dones, ro + col0 + 4, total_elems);
+                if (col0 + W < horizon) {
+                    vv[W] = ldg_chk(values, ro + col0 + W, total_elems);
+                    rr[W] = ldg_chk(rewards, ro + col0 + W, total_elems);
+                    dd[W] = ldg_chk(dones, ro + col0 + W, total_elems);
                 }
             }
-            // local composition over the (up to) four steps, latest column first
+            // local composition over the (up to) W steps, latest column first
             float K = 1.0f, D = 0.0f;
-            float dl[4], kk[4];
 #pragma unroll
-            for (int i = 3; i >= 0; --i) {
+            for (int i = W - 1; i >= 0; --i) {
                 const bool step = live && (col0 + i + 1 < horizon);   // t <= H-2
                 const float nn = __fsub_rn(1.0f, dd[i + 1]);
                 const float rho = fminf(ww[i], rho_clip);
                 const float c = fminf(ww[i], c_clip);
                 const float td = __fsub_rn(__fadd_rn(rr[i + 1], __fmul_rn(__fmul_rn(gamma, vv[i + 1]), nn)), vv[i]);
                 const float gc = __fmul_rn(gl, c);
-                dl[i] = step ? __fmul_rn(rho, td) : 0.0f;
-                kk[i] = step ? __fmul_rn(gc, nn) : 1.0f;
+                const float dl = step ? __fmul_rn(rho, td) : 0.0f;
+                const float kk = step ? __fmul_rn(gc, nn) : 1.0f;
                 gain = step ? fmaxf(gain, fabsf(gc)) : gain;
-                D = fmaf(kk[i], D, dl[i]);
-                K = kk[i] * K;
+                D = fmaf(kk, D, dl);
+                K = kk * K;
             }
             // inclusive prefix scan over j inside the warp
             float Ki = K, Di = D;
@@ -155,9 +162,9 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
             // replay in the reference's operation order
             float a_run = a_in, abs_loc = 0.0f;
             chk += fabsf(a_in);
-            float out[4];
+            float out[W];
 #pragma unroll
-            for (int i = 3; i >= 0; --i) {
+            for (int i = W - 1; i >= 0; --i) {
                 const bool step = live && (col0 + i + 1 < horizon);
                 if (step) {
                     a_run = adv_step(vv[i], ww[i], vv[i + 1], rr[i + 1], dd[i + 1], a_run, gamma, gl,
@@ -167,12 +174,16 @@ puff_adv_scan_kernel(const float* __restrict__ values, const float* __restrict__
                 out[i] = a_run;
             }
             if (live) {
-                if (VEC && col0 + 4 < horizon) {
-                    stg4_chk(advantages, ro + col0, total_elems, make_float4(out[0], out[1], out[2], out[3]));
-                } else {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if (col0 + i + 1 < horizon) stg_chk(advantages, ro + col0 + i, total_elems, out[i]);
+                for (int u = 0; u < UPT; ++u) {
+                    if (VEC && col0 + 4 * u + 4 < horizon) {
+                        stg4_chk(advantages, ro + col0 + 4 * u, total_elems,
+                                 make_float4(out[4 * u], out[4 * u + 1], out[4 * u + 2], out[4 * u + 3]));
+                    } else {
+#pragma unroll
+                        for (int i = 4 * u; i < 4 * u + 4; ++i)
+                            if (col0 + i + 1 < horizon) stg_chk(advantages, ro + col0 + i, total_elems, out[i]);
+                    }
                 }
             }
             if (seg_abs_sum != nullptr) {
