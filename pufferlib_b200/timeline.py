@@ -134,6 +134,11 @@ def run(name, launches=50):
             return
         t0 = t[:, 0].min()
         print(f"{len(t)} CTAs stamped; ns after the earliest CTA start (min / median / max over CTAs):")
+        if kernel == "bulk1d":
+            mhz = 1e3 * t[:, 9] / np.maximum(t[:, 10] - t[:, 0], 1)
+            print(f"SM clock while the CTAs ran (clock64 / %globaltimer): median {np.median(mhz):.0f} MHz")
+            print(f"chain loop of the first tile: median {np.median(t[:, 8]):.0f} cycles for {H - 1} steps "
+                  f"({np.median(t[:, 8]) / max(H - 1, 1):.1f} per step)")
         for i, nm in enumerate(names):
             if nm is None:
                 continue
