@@ -651,8 +651,9 @@ extern "C" int puff_advantage_sm100_inject_status(int value)
 }
 
 #ifdef PUFF_TIMELINE
-// Debug builds only: copies the per-CTA phase stamps (kTimelineSlots per CTA, nanoseconds of
-// %globaltimer) of the most recent instrumented launch into `out`.
+// Debug builds only: copies the per-CTA phase stamps (kTimelineSlots per CTA: clock64 values or
+// cycle totals, %globaltimer anchors in slots 12 and 14) of the most recent instrumented launch
+// into `out`.
 extern "C" int puff_advantage_sm100_timeline(unsigned long long* out, int ctas)
 {
     if (ctas > kTimelineCtas) ctas = kTimelineCtas;

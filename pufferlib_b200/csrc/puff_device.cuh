@@ -14,19 +14,26 @@ namespace puff {
 // Device-side status word: PUFF_ERR_DEVICE_WAIT when a bounded wait gave up.
 __device__ int g_device_status = 0;
 
-// Optional per-CTA timeline (compile with -DPUFF_TIMELINE): %globaltimer stamps at the phase
-// boundaries of the small-buffer kernels, read back with puff_advantage_sm100_timeline().
+// Optional per-CTA timeline (compile with -DPUFF_TIMELINE): clock64 stamps at the phase boundaries
+// of the small-buffer kernels, read back with puff_advantage_sm100_timeline().  Stamp 0 (CTA start)
+// and stamp 10 (CTA end) also record %globaltimer, in slots 12 and 14, so that the host can turn
+// cycles into nanoseconds on a time line common to all CTAs.  A stamp is a one-lane branch: the warp
+// may stay split behind it, and a split warp was measured to run a dependent chain at 37-40 cycles
+// a step instead of 19, so latency-critical code behind a stamp starts with __syncwarp().
 // Compiled out of release builds.
 #ifdef PUFF_TIMELINE
-constexpr int kTimelineSlots = 12;
+constexpr int kTimelineSlots = 16;
 constexpr int kTimelineCtas = 2048;
 __device__ unsigned long long g_timeline[kTimelineCtas * kTimelineSlots];
 #define PUFF_STAMP(slot)                                                                         \
     do {                                                                                         \
         if ((threadIdx.x & 31) == 0 && blockIdx.x < kTimelineCtas) {                             \
-            unsigned long long t_;                                                               \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                               \
-            g_timeline[blockIdx.x * kTimelineSlots + (slot)] = t_;                               \
+            if ((slot) == 0 || (slot) == 10) {                                                   \
+                unsigned long long t_;                                                           \
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                           \
+                g_timeline[blockIdx.x * kTimelineSlots + 12 + ((slot) == 10 ? 2 : 0)] = t_;      \
+            }                                                                                    \
+            g_timeline[blockIdx.x * kTimelineSlots + (slot)] = static_cast<unsigned long long>(clock64()); \
         }                                                                                        \
     } while (0)
 // cycle accounting of a warp's loop phases: PUFF_TICK(acc) adds the cycles since the previous

@@ -43,8 +43,6 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
                        int horizon, int tile_rows, long long num_tiles, int zero_last)
 {
     if (threadIdx.x == 0) PUFF_STAMP(0);   // CTA start
-    [[maybe_unused]] long long cy_cta = 0;
-    PUFF_TICK_DECL;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     float* const smem_f = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
@@ -185,13 +183,13 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
             const bool mine = lane < rows;
             float a_run = 0.0f, abs_run = 0.0f;
             bool literal = any_nonbin;
+            // a warp that a one-lane branch above left split runs the dependent chain twice as slowly
+            __syncwarp();
             [[maybe_unused]] const long long chain_t0 = clock64();
             if (!literal) {
                 if (mine) {
                     // plain accesses, scheduled by the compiler (measured no slower here than the
-                    // explicit prefetch of chain_pairs_row).  In place the loop runs at about 36
-                    // cycles a step, with or without neighbours on the SM and with or without
-                    // programmatic dependent launch; the same loop alone in a test kernel takes 17.
+                    // explicit prefetch of chain_pairs_row): 18-20 cycles a step
                     int t = horizon - 2;
                     for (; t >= 7; t -= 8) {   // eight steps' operands first, then the dependent part
                         float2 p8[8];
@@ -250,11 +248,7 @@ puff_adv_bulk1d_kernel(const float* __restrict__ values, const float* __restrict
     }
     if (tid == 0) bulk_wait_read<0>();   // the last store has left shared memory
     if (failed && tid == 0) atomicExch(&g_device_status, PUFF_ERR_DEVICE_WAIT);
-    PUFF_TICK(cy_cta);
-    if (tid == 0) {
-        PUFF_PUT(9, cy_cta);   // SM cycles between the first and the last stamp: the clock the CTA ran at
-        PUFF_STAMP(10);
-    }
+    if (tid == 0) PUFF_STAMP(10);
 }
 
 // ---------------------------------------------------------------------------

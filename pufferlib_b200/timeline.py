@@ -9,9 +9,10 @@ Builds the kernel library with -DPUFF_TIMELINE into a scratch folder (the
 release library is not touched), runs the workload's kernel back to back from a
 CUDA graph, and reads the stamps back through puff_advantage_sm100_timeline:
 
-* single-warp tma2d / one-stage bulk1d kernels: %globaltimer at the phase
-  boundaries of every CTA's first tile (nanoseconds, relative to the earliest
-  CTA start of the last launch), shown as min / median / max over the CTAs;
+* single-warp tma2d / one-stage bulk1d kernels: clock64 at the phase boundaries
+  of every CTA's first tile, turned into nanoseconds relative to the earliest
+  CTA start of the last launch through %globaltimer anchors at each CTA's first
+  and last stamp; shown as min / median / max over the CTAs;
 * warp-specialised kernels: clock64 totals of the loop phases of the chain warp,
   one terms warp (and, for bulk1d, the producer), per work item (a 32 x 32
   chunk for tma2d, a tile for bulk1d).
@@ -29,7 +30,7 @@ import torch
 from . import build, cabi
 from .workloads import WORKLOADS, Workload, make_inputs
 
-SLOTS = 12
+SLOTS = 16
 EXTRA = {"drive": Workload("drive", 8192, 91, gamma=0.98, lam=0.95, seed=7),
          "odd_large": Workload("odd_large", 131072, 127, seed=8)}
 
@@ -101,9 +102,9 @@ def run(name, launches=50):
         buf = (ctypes.c_ulonglong * (SLOTS * ctas))()
         assert lib.puff_advantage_sm100_timeline(buf, ctas) == 0
         t = np.array(buf, dtype=np.int64).reshape(ctas, SLOTS)
-        t = t[t[:, 0] != 0]
-        # slot 8 holds an item count in the warp-specialised kernel and a %globaltimer stamp otherwise
-        ws = kernel == "tma2d" and len(t) > 0 and 0 < np.median(t[:, 8]) < 1e9
+        t = t[(t != 0).any(axis=1)]
+        # slot 8 holds an item count in the warp-specialised tma2d kernel and a clock64 stamp otherwise
+        ws = kernel == "tma2d" and len(t) > 0 and 0 < np.median(t[:, 8]) < 1e7
         if ws:
             t = t[t[:, 8] > 0]
             items = t[:, 8].astype(np.float64)
@@ -128,23 +129,25 @@ def run(name, launches=50):
         if names is None:
             print("no timeline stamps in this kernel")
             return
-        t = t[t[:, 10] > 0]
+        t = t[(t[:, 10] > 0) & (t[:, 12] > 0) & (t[:, 14] > t[:, 12])]
         if len(t) == 0:
             print("this kernel form carries no timeline stamps")
             return
-        t0 = t[:, 0].min()
-        print(f"{len(t)} CTAs stamped; ns after the earliest CTA start (min / median / max over CTAs):")
+        # stamps are clock64 values; slots 12 and 14 hold %globaltimer at the first and the last stamp
+        ghz = (t[:, 10] - t[:, 0]) / (t[:, 14] - t[:, 12]).astype(np.float64)
+        t0 = t[:, 12].min()
+        print(f"{len(t)} CTAs stamped, SM clock {1e3 * np.median(ghz):.0f} MHz; ns after the earliest CTA start "
+              "(min / median / max over CTAs):")
         if kernel == "bulk1d":
-            mhz = 1e3 * t[:, 9] / np.maximum(t[:, 10] - t[:, 0], 1)
-            print(f"SM clock while the CTAs ran (clock64 / %globaltimer): median {np.median(mhz):.0f} MHz")
             print(f"chain loop of the first tile: median {np.median(t[:, 8]):.0f} cycles for {H - 1} steps "
                   f"({np.median(t[:, 8]) / max(H - 1, 1):.1f} per step)")
         for i, nm in enumerate(names):
             if nm is None:
                 continue
-            col = t[:, i][t[:, i] > 0] - t0
-            if len(col):
-                print(f"  {nm:45s} {col.min():7d} {int(np.median(col)):7d} {col.max():7d}")
+            ok = t[:, i] > 0
+            if ok.any():
+                col = (t[ok, 12] - t0) + (t[ok, i] - t[ok, 0]) / ghz[ok]
+                print(f"  {nm:45s} {col.min():7.0f} {np.median(col):7.0f} {col.max():7.0f}")
 
 
 if __name__ == "__main__":
