@@ -333,7 +333,7 @@ int puff_advantage_sm100_inject_status(int value);
 #define PUFF_TUNE_WS_STAGES     2   /* PUFF_ADV_WS: 0 = single-warp tma2d, N = warp-specialised with N stages */
 #define PUFF_TUNE_CTAS_PER_SM   3   /* PUFF_ADV_CTAS_PER_SM: cap on resident CTAs per SM of the tma2d kernels */
 #define PUFF_TUNE_LOAD_GROUP    4   /* PUFF_ADV_GROUP: chunks whose loads the warp-specialised producer issues together */
-#define PUFF_TUNE_SCAN_THREADS  5   /* PUFF_ADV_SCAN_THREADS: threads per row of the scan kernel (power of two, 32..1024) */
+#define PUFF_TUNE_SCAN_THREADS  5   /* PUFF_ADV_SCAN_THREADS: threads per row of the scan kernel (power of two, 32..1024; default by row count and horizon) */
 #define PUFF_TUNE_RESERVE_SMS   6   /* PUFF_ADV_RESERVE_SMS: SMs the persistent (warp-specialised) grids leave free for other streams' kernels */
 #define PUFF_TUNE_TILE_ROWS     7   /* PUFF_ADV_TILE_ROWS: cap on the rows per tile of the bulk1d kernels (4, 8, 16, 32) */
 #define PUFF_TUNE_PDL           8   /* PUFF_ADV_PDL: 0 = launch without programmatic stream serialization */

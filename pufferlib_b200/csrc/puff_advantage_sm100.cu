@@ -549,9 +549,24 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
         // share an SM, so 256 rows of 4096 columns run as one wave).  A thread takes four columns
         // per pass, or eight when the row would otherwise need a second pass: half the scans and
         // barriers, and all of a thread's loads in flight at once.
+        // Threads per row.  Few rows: as many as the row has 4-column units, up to 512, so that the
+        // SMs are busy at all (256 x 4096: 6.8 us with 512, 7.7 with 256, 9.7 with 128).  Many rows:
+        // fewer threads per row, so that several rows are in flight per SM and one row's loads
+        // overlap the others' scans -- as many as keep all rows resident at once, but no fewer than
+        // one eight-column pass needs (or 128).  Measured: 2048 x 4096 34.3 us with 512 threads per
+        // row, 29.4 with 128; 3000 x 1024 15.3 / 12.0; 512 x 4096 11.4 / 10.2 (256); 3500 x 512
+        // 8.9 (128) / 8.1 (64).
         const long long units4 = (horizon + 3) / 4;
         int nt = 32;
         while (nt < 512 && nt < units4) nt <<= 1;
+        {
+            int cap = 512;
+            while (cap > 32 && static_cast<long long>(cap) * num_segments > 1280LL * dev->sm_count) cap >>= 1;
+            int floor_nt = 32;   // threads of one eight-column pass, at most 128
+            while (floor_nt < 128 && 2LL * floor_nt < units4) floor_nt <<= 1;
+            if (cap < floor_nt) cap = floor_nt;
+            if (nt > cap) nt = cap;
+        }
         {
             const int o = tune(PUFF_TUNE_SCAN_THREADS, 0);
             if (o >= 32 && o <= 1024 && (o & (o - 1)) == 0) nt = o;

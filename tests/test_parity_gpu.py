@@ -135,6 +135,23 @@ def test_config_scan_tolerance(name):
     np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("S,H", [(3000, 1024), (3500, 512), (700, 2048), (512, 4096), (2048, 4096), (8192, 512),
+                                 (1537, 1030), (2999, 515)])
+def test_scan_with_many_rows_within_tolerance(S, H):
+    """With many rows the launcher gives a row fewer threads (512 down to 64, one or several
+    eight- or four-column passes); every such split keeps the tolerance, the untouched last
+    column and the fused sums."""
+    wl = Workload("scan_rows", S, H, gamma=0.999, lam=0.95, done_p=0.002, seed=S + H)
+    inputs = [t.numpy() for t in make_inputs(wl)]
+    got, abs_sum, kernel = run_gpu(inputs, wl.hyper(), "scan", epilogue=True)
+    assert kernel == "scan"
+    want = oracle_advantage(inputs, wl.hyper())
+    assert np.all(got[:, -1] == np.float32(SENTINEL))
+    assert within_scan_tolerance(got[:, :-1], want[:, :-1])
+    exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
+    np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6)
+
+
 def test_auto_variant_choices():
     picks = {}
     for name in ("cfg1", "cfg3", "cfg4"):
