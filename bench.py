@@ -23,8 +23,9 @@ entry point with pinned host inputs and outputs (copies inside the timed
 region) beside the time of its bare copies, `roofline` the advantage kernel's
 algorithmic bytes over its CUDA-event duration against the measured HBM copy
 peak, `small_workloads` (N = 1) the steady-state kernel time of the other
-configurations with a parity bit each, and `cpu_baseline` the reference CPU op
-timed on this machine's cores.
+configurations with a parity bit each, `neighbour_kernels` (N = 1) the sampler
+prologue, the minibatch gather and the rollout writer on the headline's buffer
+shape, and `cpu_baseline` the reference CPU op timed on this machine's cores.
 
 `--impl reference` times only the reference's own CPU implementation (the
 build under oracle/_ref/ when present, else the oracle port) and prints the
@@ -520,9 +521,10 @@ def run_b200_arm(args, wl, rank, local_rank, world):
         del st, local
 
     # ---- small and odd workloads: steady-state kernel time (single GPU only) -------
-    small = None
+    small = neighbours = None
     if world == 1 and not args.no_small and args.workload == "cfg2" and args.segments == 0:
         small = time_small_workloads(dev, fence)
+        neighbours = time_neighbour_kernels(dev, fence)
 
     # ---- the reference's own CUDA kernel on this GPU (secondary baseline) -----
     ref_cuda = None
@@ -628,6 +630,8 @@ def run_b200_arm(args, wl, rank, local_rank, world):
             line["strong_scaling"] = strong
         if small is not None:
             line["small_workloads"] = small
+        if neighbours is not None:
+            line["neighbour_kernels"] = neighbours
         if cpu_line is not None:
             line["cpu_baseline"] = cpu_line
         print(json.dumps(line), flush=True)
@@ -713,6 +717,114 @@ def time_small_workloads(dev, fence):
     floor = 1e3 * t0.elapsed_time(t1) / 200
     for row in rows:
         row["launch_floor_us"] = floor
+    return rows
+
+
+def time_neighbour_kernels(dev, fence):
+    """Steady-state device time of the kernels either side of the advantage op, on cfg2's
+    buffer shape: the sampler prologue (priority weights + probabilities, pufferl.py:359-361),
+    the minibatch gather with its normalisation (:363-375, 408-409; 8192 sampled segments)
+    and the rollout writer (:275, 294-296).  Each is a CUDA graph of back-to-back calls
+    through the C ABI, rotating over buffer sets that together exceed 2x L2."""
+    from pufferlib_b200 import cabi
+    lib = cabi.load()
+    peak, _ = hbm_peak()
+    S, H, M = 131072, 256, 8192
+    gen = torch.Generator(device="cpu").manual_seed(11)
+    stream = torch.cuda.Stream()
+
+    def timed(launch, n):
+        with torch.cuda.stream(stream):
+            for i in range(min(n, 8)):
+                launch(i)
+        fence()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(n):
+                launch(i)
+        g.replay()
+        fence()
+        times = []
+        for _ in range(5):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            g.replay()
+            t1.record()
+            torch.cuda.synchronize()
+            times.append(t0.elapsed_time(t1) / n)
+        return 1e3 * statistics.median(times)
+
+    def st():
+        return torch.cuda.current_stream().cuda_stream
+
+    rows = []
+    # --- minibatch gather + normalisation ---
+    adv = torch.randn((S, H), generator=gen).to(dev)
+    val = torch.randn((S, H), generator=gen).to(dev)
+    probs = torch.rand(S, generator=gen).to(dev)
+    probs /= probs.sum()
+    n_sets = rotation_sets(7 * 4 * M * H)
+    idx = [torch.randint(0, S, (M,), generator=gen).to(dev) for _ in range(n_sets)]
+    outs = [[torch.empty((M, H), device=dev) for _ in range(4)] + [torch.empty(M, device=dev)] for _ in range(n_sets)]
+    mb_scratch = torch.empty(lib.puff_minibatch_sm100_scratch_bytes(M) // 8 + 1, dtype=torch.float64, device=dev)
+
+    def gather(i):
+        o = outs[i % n_sets]
+        cabi.check(lib.puff_minibatch_sm100_gather_ex(
+            adv.data_ptr(), val.data_ptr(), probs.data_ptr(), idx[i % n_sets].data_ptr(), o[0].data_ptr(),
+            o[1].data_ptr(), o[2].data_ptr(), o[3].data_ptr(), o[4].data_ptr(), 0.5, S, S, H, M,
+            mb_scratch.data_ptr(), mb_scratch.numel() * 8, st()))
+
+    us = timed(gather, max(n_sets, 100))
+    mb_bytes = 7 * 4 * M * H
+    rows.append({"kernels": "puff_mb_gather_kernel + puff_mb_normalize_kernel",
+                 "what": f"minibatch gather + normalisation, {M} of {S} segments x {H}",
+                 "us_per_call": us, "algorithmic_bytes": mb_bytes, "gbs": mb_bytes / (us * 1e-6) / 1e9,
+                 "frac": mb_bytes / (us * 1e-6) / 1e9 / peak,
+                 "bytes": "28 B per gathered element: 8 read + 12 written by the gather, 4 read + 4 written "
+                          "by the normalisation", "buffer_sets": n_sets})
+    del outs, idx
+
+    # --- sampler prologue: weights, total, probabilities ---
+    sums = torch.rand(S, generator=gen).to(dev)
+    n_sets = rotation_sets(16 * S)
+    n_sets = min(n_sets, 64)   # 2 MB per call: L2-resident in any trainer, so no attempt to defeat L2 beyond this
+    wts = [torch.empty(S, device=dev) for _ in range(n_sets)]
+    prb = [torch.empty(S, device=dev) for _ in range(n_sets)]
+    total = torch.empty(1, dtype=torch.float64, device=dev)
+    pr_scratch = torch.empty(lib.puff_priorities_sm100_scratch_bytes(S) // 8 + 1, dtype=torch.float64, device=dev)
+
+    def prologue(i):
+        cabi.check(lib.puff_priorities_sm100_weights(sums.data_ptr(), wts[i % n_sets].data_ptr(), total.data_ptr(), 0.6, S,
+                                                     pr_scratch.data_ptr(), pr_scratch.numel() * 8, st()))
+        cabi.check(lib.puff_priorities_sm100_probs(wts[i % n_sets].data_ptr(), total.data_ptr(), prb[i % n_sets].data_ptr(),
+                                                   S, st()))
+
+    us = timed(prologue, 200)
+    rows.append({"kernels": "puff_prio_weights_kernel + puff_prio_total_kernel + puff_prio_probs_kernel",
+                 "what": f"sampler prologue: weights, their total, probabilities over {S} segments",
+                 "us_per_call": us, "algorithmic_bytes": 16 * S, "gbs": 16 * S / (us * 1e-6) / 1e9,
+                 "frac": 16 * S / (us * 1e-6) / 1e9 / peak,
+                 "bytes": "16 B per segment; three dependent launches, latency-bound"})
+
+    # --- rollout writer: one environment step into one column ---
+    rew, ter = torch.zeros((S, H), device=dev), torch.zeros((S, H), device=dev)
+    s_r, s_v = torch.randn(S, generator=gen).to(dev), torch.randn(S, generator=gen).to(dev)
+    s_d = (torch.rand(S, generator=gen) < 0.01).to(dev)
+
+    def rollout(i):
+        cabi.check(lib.puff_rollout_sm100_write(rew.data_ptr(), ter.data_ptr(), val.data_ptr(), s_r.data_ptr(),
+                                                s_d.data_ptr(), s_v.data_ptr(), 0, S, i % H, S, H, 1.0, st()))
+
+    us = timed(rollout, 256)
+    ro_bytes = S * (9 + 12)
+    rows.append({"kernels": "puff_rollout_write_kernel",
+                 "what": f"rollout writer: one step of {S} environments into one column of three [S, {H}] buffers",
+                 "us_per_call": us, "algorithmic_bytes": ro_bytes, "gbs": ro_bytes / (us * 1e-6) / 1e9,
+                 "frac": ro_bytes / (us * 1e-6) / 1e9 / peak,
+                 "bytes": "9 B read + 12 B written per environment; the writes are 4-byte column elements of "
+                          "1 KB rows, one 32-byte sector each"})
+    assert cabi.device_status() == 0
     return rows
 
 

@@ -248,26 +248,10 @@ static int persistent_sms(int sm_count)
     return n < 1 ? 1 : n;
 }
 
-// Every advantage kernel is launched with the programmatic-stream-serialization attribute (unless
-// PUFF_TUNE_PDL is 0): its set-up may then overlap the tail of whatever precedes it in the stream,
-// and it waits (pdl_wait in the kernels) for that predecessor to complete before it touches a tensor.
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st,
-                                 Args... args)
-{
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(grid));
-    cfg.blockDim = dim3(static_cast<unsigned>(block));
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = tune(PUFF_TUNE_PDL, 1) != 0 ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
-
+// Every advantage kernel is launched through launch_kernel() (puff_launch.cuh) with the
+// programmatic-stream-serialization attribute (unless PUFF_TUNE_PDL is 0): its set-up may then
+// overlap the tail of whatever precedes it in the stream, and it waits (pdl_wait in the kernels)
+// for that predecessor to complete before it touches a tensor.
 template <int NST>
 static cudaError_t launch_tma2d(const MapSet& m, const float* adv_in, float* seg_abs_sum, float gamma, float lambda, float rho_clip,
                                 float c_clip, long long rows, int horizon, int grid, int tiles, cudaStream_t st)
@@ -626,6 +610,7 @@ extern "C" long long puff_advantage_sm100_launch_count(void)
 
 namespace puff {
 void count_launch() { g_launch_count.fetch_add(1, std::memory_order_relaxed); }
+int tune_value(int knob, int fallback) { return tune(knob, fallback); }
 }
 
 namespace puff {

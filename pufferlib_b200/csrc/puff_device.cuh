@@ -8,6 +8,7 @@
 #include <stdint.h>
 
 #include "../../include/puff_advantage.h"
+#include "puff_launch.cuh"
 
 namespace puff {
 
@@ -254,22 +255,6 @@ __device__ __forceinline__ void bulk_wait_read()
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
-}
-// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
-// attribute may start while its predecessor in the stream is still running: its CTAs become
-// resident as soon as every CTA of the predecessor has executed launch_dependents (or exited) and
-// resources allow.  pdl_wait() then blocks until the predecessor grid has completed and its
-// memory operations are visible, so everything before it must touch no global memory that an
-// earlier kernel may still read or write: only the kernel's own set-up (shared-memory carve-up,
-// mbarrier initialisation, fetching the tensor-map descriptors, which are kernel parameters)
-// overlaps the predecessor's tail.  Both are no-ops in a launch without the attribute.
-__device__ __forceinline__ void pdl_wait()
-{
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-}
-__device__ __forceinline__ void pdl_launch_dependents()
-{
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 __device__ __forceinline__ float4 lds128(uint32_t addr)
 {

@@ -16,6 +16,7 @@
 #include <new>
 
 #include "../../include/puff_advantage.h"
+#include "puff_launch.cuh"
 
 namespace puff {
 void count_launch();
@@ -48,6 +49,8 @@ puff_prio_weights_kernel(const float* __restrict__ seg_abs_sum, float* __restric
                          double* __restrict__ partial, float alpha, long long num_segments)
 {
     __shared__ double s_part[kPrioThreads / 32];
+    pdl_wait();
+    pdl_launch_dependents();
     // contiguous slab per CTA, so the partial does not depend on the grid-stride order
     const long long per = (num_segments + gridDim.x - 1) / gridDim.x;
     const long long lo = per * blockIdx.x;
@@ -67,6 +70,8 @@ __global__ void PUFF_PRIO_BOUNDS
 puff_prio_total_kernel(const double* __restrict__ partial, int n, double* __restrict__ total_w)
 {
     __shared__ double s_part[kPrioThreads / 32];
+    pdl_wait();
+    pdl_launch_dependents();
     double acc = 0.0;
     for (int i = threadIdx.x; i < n; i += blockDim.x) acc += partial[i];
     const double tot = block_sum(acc, s_part);
@@ -77,6 +82,8 @@ __global__ void PUFF_PRIO_BOUNDS
 puff_prio_probs_kernel(const float* __restrict__ weights, const double* __restrict__ total_w,
                        float* __restrict__ probs, long long num_segments)
 {
+    pdl_wait();
+    pdl_launch_dependents();
     // pufferl.py:361 evaluates in fp32: (w + 1e-6) / (sum + 1e-6)
     const float denom = static_cast<float>(*total_w) + 1e-6f;
     for (long long s = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; s < num_segments;
@@ -237,13 +244,13 @@ extern "C" int puff_priorities_sm100_weights(const float* seg_abs_sum, float* we
         return PUFF_ERR_WORKSPACE;
     const int blocks = prio_blocks(num_segments);
     double* partial = static_cast<double*>(scratch);
-    puff_prio_weights_kernel<<<blocks, kPrioThreads, 0, st>>>(seg_abs_sum, weights, partial, alpha, num_segments);
+    cudaError_t e = launch_kernel(puff_prio_weights_kernel, blocks, kPrioThreads, 0, st, seg_abs_sum, weights, partial,
+                                  alpha, num_segments);
     count_launch();
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return static_cast<int>(e);
-    puff_prio_total_kernel<<<1, kPrioThreads, 0, st>>>(partial, blocks, total_w);
+    e = launch_kernel(puff_prio_total_kernel, 1, kPrioThreads, 0, st, partial, blocks, total_w);
     count_launch();
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(e);
 }
 
 extern "C" int puff_priorities_sm100_probs(const float* weights, const double* total_w, float* probs,
@@ -255,9 +262,10 @@ extern "C" int puff_priorities_sm100_probs(const float* weights, const double* t
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     long long blocks = (num_segments + kPrioThreads - 1) / kPrioThreads;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    puff_prio_probs_kernel<<<static_cast<int>(blocks), kPrioThreads, 0, st>>>(weights, total_w, probs, num_segments);
+    const cudaError_t e = launch_kernel(puff_prio_probs_kernel, static_cast<int>(blocks), kPrioThreads, 0, st, weights,
+                                        total_w, probs, num_segments);
     count_launch();
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(e);
 }
 
 // ---------------------------------------------------------------------------
