@@ -15,7 +15,10 @@
 // forms mean and std, and writes the weighted, normalised advantages.  The raw
 // rows it re-reads were written a few microseconds earlier and come from L2.
 // Memory-bound gathers of whole rows: 8 bytes read and 12-16 written per
-// gathered element.
+// gathered element.  (Both steps as ONE cooperative launch with a grid-wide
+// barrier between them, the first rows kept in registers across it, measured
+// 18.3 us where the two launches below, chained by programmatic dependent
+// launch, take 15.5: 8192 of 131072 x 256 rows.)
 #include <cuda_runtime.h>
 #include <stdint.h>
 

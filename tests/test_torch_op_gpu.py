@@ -213,7 +213,8 @@ def test_standalone_nvcc_harness(tmp_path):
     assert "OK" in out.stdout
 
 
-@pytest.mark.parametrize("S,H,M", [(8192, 64, 512), (1000, 91, 333), (64, 256, 64), (50, 1, 7), (300, 128, 1)])
+@pytest.mark.parametrize("S,H,M", [(8192, 64, 512), (1000, 91, 333), (64, 256, 64), (50, 1, 7), (300, 128, 1),
+                                   (8192, 256, 8192), (20000, 512, 12000), (4096, 260, 5000), (3000, 8, 9000)])
 def test_minibatch_gather_matches_oracle_and_torch(S, H, M):
     """pufferl.py:363, 373-375, 408-409 fused: against the fp64 oracle and the
     eager torch sequence on the same device."""
@@ -225,7 +226,7 @@ def test_minibatch_gather_matches_oracle_and_torch(S, H, M):
     val = torch.randn(S, H, generator=g)
     probs = torch.rand(S, generator=g) + 0.01
     probs = probs / probs.sum()
-    idx = torch.multinomial(probs, M, generator=g)
+    idx = torch.multinomial(probs, M, replacement=M > S, generator=g)
     beta = 0.35
     d_adv, d_val, d_probs, d_idx = adv.cuda(), val.cuda(), probs.cuda(), idx.cuda()
     mv, mr, ma, an, mp = pufferlib_b200.minibatch_gather(d_adv, d_val, d_probs, d_idx, beta)
