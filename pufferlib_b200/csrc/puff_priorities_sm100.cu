@@ -151,6 +151,8 @@ puff_prio_total_push_kernel(const double* __restrict__ partial, int n, ExControl
 {
     __shared__ double s_part[kPrioThreads / 32];
     __shared__ double s_total;
+    pdl_wait();
+    pdl_launch_dependents();
     double acc = 0.0;
     for (int i = threadIdx.x; i < n; i += blockDim.x) acc += partial[i];
     const double tot = block_sum(acc, s_part);
@@ -175,6 +177,8 @@ puff_prio_probs_gathered_kernel(const float* __restrict__ weights, const ExSlot*
 {
     __shared__ double s_total;
     __shared__ int s_ok;
+    pdl_wait();   // the push of this exchange, the previous kernel of the stream, has completed
+    pdl_launch_dependents();
     if (threadIdx.x < 32) {
         const unsigned long long seq = ctl->seq;    // the push of this exchange precedes this kernel in its stream
         const int lane = threadIdx.x;
@@ -462,16 +466,17 @@ extern "C" int puff_priorities_sm100_weights_push(const float* seg_abs_sum, floa
     int blocks = 0;   // a rank without rows still takes part with a total of zero
     if (num_segments > 0) {
         blocks = prio_blocks(num_segments);
-        puff_prio_weights_kernel<<<blocks, kPrioThreads, 0, st>>>(seg_abs_sum, weights, partial, alpha, num_segments);
+        const cudaError_t e = launch_kernel(puff_prio_weights_kernel, blocks, kPrioThreads, 0, st, seg_abs_sum, weights,
+                                            partial, alpha, num_segments);
         count_launch();
-        cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return static_cast<int>(e);
     }
     ExPeers peers;
     for (int r = 0; r < kExMaxWorld; ++r) peers.slots[r] = r < x->world ? x->peer[r] : nullptr;
-    puff_prio_total_push_kernel<<<1, kPrioThreads, 0, st>>>(partial, blocks, x->control, peers, x->rank, x->world);
+    const cudaError_t e = launch_kernel(puff_prio_total_push_kernel, 1, kPrioThreads, 0, st, partial, blocks, x->control,
+                                        peers, x->rank, x->world);
     count_launch();
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(e);
 }
 
 extern "C" int puff_priorities_sm100_probs_gathered(const float* weights, double* total_w, float* probs,
@@ -485,8 +490,9 @@ extern "C" int puff_priorities_sm100_probs_gathered(const float* weights, double
     long long blocks = (num_segments + kPrioThreads - 1) / kPrioThreads;
     if (blocks > 148 * 8) blocks = 148 * 8;
     if (blocks < 1) blocks = 1;       // the total is still gathered (and written) for a rank without rows
-    puff_prio_probs_gathered_kernel<<<static_cast<int>(blocks), kPrioThreads, 0, st>>>(
-        weights, x->mailbox, x->control, total_w, probs, num_segments, x->world, x->wait_ns, x->status);
+    const cudaError_t e = launch_kernel(puff_prio_probs_gathered_kernel, static_cast<int>(blocks), kPrioThreads, 0, st,
+                                        weights, x->mailbox, x->control, total_w, probs, num_segments, x->world,
+                                        x->wait_ns, x->status);
     count_launch();
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(e);
 }

@@ -339,6 +339,52 @@ def test_op_replays_from_a_cuda_graph():
         np.testing.assert_allclose(sums.cpu().numpy(), exact, rtol=1e-5, atol=1e-6)
 
 
+def test_dependent_launches_back_to_back_keep_stream_order():
+    """Every kernel of the sampler sequence is launched with programmatic stream
+    serialization and waits for its predecessor before its first global access.  The
+    sequence advantage -> weights -> probabilities -> gather, issued many times without
+    a synchronise in between (eagerly and from one CUDA graph), gives what the same calls
+    give one at a time."""
+    import pufferlib_b200
+    S, H, M, rounds = 4096, 64, 512, 24
+    wl = Workload("chain", S, H, seed=21)
+    hyper = wl.hyper()
+    gen = torch.Generator().manual_seed(5)
+    base = [t.cuda() for t in make_inputs(wl)]
+    scales = [1.0 + 0.03125 * i for i in range(rounds)]
+    inputs = [[base[0] * sc, base[1] * sc, base[2], base[3]] for sc in scales]
+    idx = [torch.randint(0, S, (M,), generator=gen).cuda() for _ in range(rounds)]
+
+    def one(i):
+        sums = torch.empty(S, device="cuda")
+        adv = pufferlib_b200.compute_puff_advantage_fill(*inputs[i], *hyper, seg_abs_sum=sums)
+        w, total = pufferlib_b200.priority_weights(sums, 0.6)
+        probs = pufferlib_b200.priority_probs(w, total)
+        out = pufferlib_b200.minibatch_gather(adv, inputs[i][0], probs, idx[i], 0.4)
+        return [adv, probs] + list(out)
+
+    want = []
+    for i in range(rounds):
+        want.append([t.clone() for t in one(i)])
+        torch.cuda.synchronize()
+    got = [one(i) for i in range(rounds)]           # no synchronise between the calls
+    torch.cuda.synchronize()
+    for i in range(rounds):
+        for a, b in zip(got[i], want[i]):
+            assert torch.equal(a, b), i
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        got = [one(i) for i in range(rounds)]
+    for t in (x for row in got for x in row):
+        t.fill_(SENTINEL)
+    g.replay()
+    torch.cuda.synchronize()
+    for i in range(rounds):
+        for a, b in zip(got[i], want[i]):
+            assert torch.equal(a, b), i
+
+
 def test_concurrent_launches_from_threads_and_streams():
     """The launcher is re-entrant: per-thread tensor-map caches, one-time device
     set-up behind a lock.  Four threads, each on its own stream and buffers."""
