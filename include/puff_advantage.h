@@ -336,7 +336,7 @@ int puff_advantage_sm100_inject_status(int value);
 #define PUFF_TUNE_SCAN_THREADS  5   /* PUFF_ADV_SCAN_THREADS: threads per row of the scan kernel (power of two, 32..1024; default by row count and horizon) */
 #define PUFF_TUNE_RESERVE_SMS   6   /* PUFF_ADV_RESERVE_SMS: SMs the persistent (warp-specialised) grids leave free for other streams' kernels */
 #define PUFF_TUNE_TILE_ROWS     7   /* PUFF_ADV_TILE_ROWS: cap on the rows per tile of the bulk1d kernels (4, 8, 16, 32) */
-#define PUFF_TUNE_PDL           8   /* PUFF_ADV_PDL: 0 = launch without programmatic stream serialization */
+#define PUFF_TUNE_PDL           8   /* PUFF_ADV_PDL: 0 = launch without programmatic stream serialization, 2 = only the advantage kernels with it */
 #define PUFF_TUNE_SCAN_WIDE     9   /* PUFF_ADV_SCAN_WIDE: 0 = the scan kernel always takes four columns per thread and pass */
 #define PUFF_TUNE_COUNT        10
 int puff_advantage_sm100_set_tuning(int knob, int value);

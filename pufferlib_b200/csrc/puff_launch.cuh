@@ -28,10 +28,11 @@ __device__ __forceinline__ void pdl_launch_dependents()
 
 int tune_value(int knob, int fallback);   // puff_advantage_sm100.cu: a PUFF_TUNE_* knob, or the fallback while unset
 
-// Launch with the programmatic-stream-serialization attribute (unless PUFF_TUNE_PDL is 0).
+// Launch with the programmatic-stream-serialization attribute.  PUFF_TUNE_PDL: 1 (default) every
+// kernel that comes through here, 2 only the advantage kernels (`core`), 0 none.
 template <typename... KArgs, typename... Args>
-static cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st,
-                                 Args... args)
+static cudaError_t launch_with_pdl(bool core, void (*kernel)(KArgs...), int grid, int block, size_t smem,
+                                   cudaStream_t st, Args... args)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
@@ -42,8 +43,23 @@ static cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int block, 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = tune_value(PUFF_TUNE_PDL, 1) != 0 ? 1 : 0;
+    const int mode = tune_value(PUFF_TUNE_PDL, 1);
+    cfg.numAttrs = (mode == 1 || (mode == 2 && core)) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+// the advantage kernels
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st,
+                                 Args... args)
+{
+    return launch_with_pdl(true, kernel, grid, block, smem, st, args...);
+}
+// the kernels either side of the op (sampler prologue, exchange, minibatch gather, rollout writer)
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_neighbour(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st,
+                                    Args... args)
+{
+    return launch_with_pdl(false, kernel, grid, block, smem, st, args...);
 }
 
 }  // namespace puff

@@ -273,18 +273,23 @@ extern "C" int puff_minibatch_sm100_gather_ex(const float* advantages, const flo
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     const int blocks = mb_blocks(mb_segments);
     double* partial = static_cast<double*>(scratch);
-    cudaError_t e = vec ? launch_kernel(puff_mb_gather_kernel<true>, blocks, kMbThreads, 0, st, advantages, values, idx,
-                                        mb_values, mb_returns, mb_adv_raw, partial, num_segments, horizon, mb_segments)
-                        : launch_kernel(puff_mb_gather_kernel<false>, blocks, kMbThreads, 0, st, advantages, values, idx,
-                                        mb_values, mb_returns, mb_adv_raw, partial, num_segments, horizon, mb_segments);
+    // the first kernel of the call is launched plainly (what precedes it in the stream is not this
+    // library's to know), the second programmatically behind the first
+    if (vec)
+        puff_mb_gather_kernel<true><<<blocks, kMbThreads, 0, st>>>(advantages, values, idx, mb_values, mb_returns,
+                                                                   mb_adv_raw, partial, num_segments, horizon, mb_segments);
+    else
+        puff_mb_gather_kernel<false><<<blocks, kMbThreads, 0, st>>>(advantages, values, idx, mb_values, mb_returns,
+                                                                    mb_adv_raw, partial, num_segments, horizon, mb_segments);
     count_launch();
+    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return static_cast<int>(e);
     long long nb = (mb_segments + 15) / 16;
     if (nb > kMbMaxBlocks) nb = kMbMaxBlocks;
-    e = vec ? launch_kernel(puff_mb_normalize_kernel<true>, static_cast<int>(nb), kMbThreads, 0, st, mb_adv_raw, prio_probs,
+    e = vec ? launch_neighbour(puff_mb_normalize_kernel<true>, static_cast<int>(nb), kMbThreads, 0, st, mb_adv_raw, prio_probs,
                             idx, partial, blocks, mb_adv_norm, mb_prio, anneal_beta, num_segments, prio_segments, horizon,
                             mb_segments)
-            : launch_kernel(puff_mb_normalize_kernel<false>, static_cast<int>(nb), kMbThreads, 0, st, mb_adv_raw, prio_probs,
+            : launch_neighbour(puff_mb_normalize_kernel<false>, static_cast<int>(nb), kMbThreads, 0, st, mb_adv_raw, prio_probs,
                             idx, partial, blocks, mb_adv_norm, mb_prio, anneal_beta, num_segments, prio_segments, horizon,
                             mb_segments);
     count_launch();

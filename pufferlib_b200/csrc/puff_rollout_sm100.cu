@@ -15,7 +15,6 @@
 #include <stdint.h>
 
 #include "../../include/puff_advantage.h"
-#include "puff_launch.cuh"
 
 namespace puff {
 void count_launch();
@@ -26,8 +25,6 @@ puff_rollout_write_kernel(float* __restrict__ rewards, float* __restrict__ termi
                           const float* __restrict__ step_values, long long row_begin, long long num_rows,
                           long long column, long long horizon, float reward_clip)
 {
-    pdl_wait();
-    pdl_launch_dependents();
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < num_rows;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const long long o = (row_begin + i) * horizon + column;
@@ -60,9 +57,9 @@ extern "C" int puff_rollout_sm100_write(float* rewards, float* terminals, float*
         if (reinterpret_cast<uintptr_t>(fp[i]) & 3u) return PUFF_ERR_ALIGN;
     long long blocks = (num_rows + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    const cudaError_t e = launch_kernel(puff_rollout_write_kernel, static_cast<int>(blocks), 256, 0,
-                                        static_cast<cudaStream_t>(cuda_stream), rewards, terminals, values, step_rewards,
-                                        step_dones, step_values, row_begin, num_rows, column, horizon, reward_clip);
+    puff_rollout_write_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        rewards, terminals, values, step_rewards, step_dones, step_values, row_begin, num_rows, column, horizon,
+        reward_clip);
     count_launch();
-    return static_cast<int>(e);
+    return static_cast<int>(cudaGetLastError());
 }
