@@ -54,7 +54,10 @@ static cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int block, 
 {
     return launch_with_pdl(true, kernel, grid, block, smem, st, args...);
 }
-// the kernels either side of the op (sampler prologue, exchange, minibatch gather, rollout writer)
+// The kernels either side of the op (sampler prologue, exchange, minibatch gather).  Used for the
+// second and later kernels of an entry point only: the first one is a plain launch, because
+// what precedes it in the stream is not this library's to know, and a programmatically launched
+// kernel behind an advantage kernel of another stream was measured to slow the pipelined step.
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_neighbour(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st,
                                     Args... args)
