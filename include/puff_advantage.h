@@ -193,7 +193,9 @@ int puff_priorities_sm100_probs(const float* weights, const double* total_w,
  *
  *   puff_priorities_sm100_weights_push   weights[s] as puff_priorities_sm100_weights,
  *             then the local fp64 total is stored into every rank's mailbox
- *             (plain stores over NVLink to peer-mapped memory, fence, flag).
+ *             (plain stores over NVLink to peer-mapped memory, fence, flag);
+ *             one launch: the CTA that finishes last adds the per-CTA sums in
+ *             index order and pushes.
  *   puff_priorities_sm100_probs_gathered  waits until all `world` totals of the
  *             current round sit in this rank's own mailbox, adds them in rank
  *             order (identical on every rank), writes the global total to
