@@ -340,7 +340,8 @@ int puff_advantage_sm100_inject_status(int value);
 #define PUFF_TUNE_TILE_ROWS     7   /* PUFF_ADV_TILE_ROWS: cap on the rows per tile of the bulk1d kernels (4, 8, 16, 32) */
 #define PUFF_TUNE_PDL           8   /* PUFF_ADV_PDL: 0 = launch without programmatic stream serialization, 2 = only the advantage kernels with it */
 #define PUFF_TUNE_SCAN_WIDE     9   /* PUFF_ADV_SCAN_WIDE: 0 = the scan kernel always takes four columns per thread and pass */
-#define PUFF_TUNE_COUNT        10
+#define PUFF_TUNE_B1_WARP_TEAMS 10  /* PUFF_ADV_B1_WARP_TEAMS: 0 = the one-stage bulk1d kernel always works with one tile per CTA, never one per warp */
+#define PUFF_TUNE_COUNT        11
 int puff_advantage_sm100_set_tuning(int knob, int value);
 /* Library version, "major.minor". */
 const char* puff_advantage_sm100_version(void);

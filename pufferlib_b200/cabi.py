@@ -85,7 +85,7 @@ def load():
 
 
 TUNE = {"force_kernel": 0, "stages": 1, "ws_stages": 2, "ctas_per_sm": 3, "load_group": 4, "scan_threads": 5,
-        "reserve_sms": 6, "tile_rows": 7, "pdl": 8, "scan_wide": 9}
+        "reserve_sms": 6, "tile_rows": 7, "pdl": 8, "scan_wide": 9, "b1_warp_teams": 10}
 
 
 def set_tuning(**knobs):

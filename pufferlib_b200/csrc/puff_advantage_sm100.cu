@@ -112,7 +112,8 @@ static const DeviceInfo* device_info(int* code)
                 set_tma2d_ws_attrs<3, 2>();
                 set_tma2d_ws_attrs<4, 2>();
                 set_tma2d_ws_attrs<6, 2>();
-                cudaFuncSetAttribute(puff_adv_bulk1d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem_optin);
+                cudaFuncSetAttribute(puff_adv_bulk1d_kernel<kB1Threads>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem_optin);
+                cudaFuncSetAttribute(puff_adv_bulk1d_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem_optin);
                 cudaFuncSetAttribute(puff_adv_bulk1d_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem_optin);
                 d.err = cudaGetLastError();
             }
@@ -223,7 +224,8 @@ static void tune_init()
         static const char* const names[PUFF_TUNE_COUNT] = {"PUFF_ADV_FORCE_KERNEL", "PUFF_ADV_STAGES", "PUFF_ADV_WS",
                                                            "PUFF_ADV_CTAS_PER_SM", "PUFF_ADV_GROUP",
                                                            "PUFF_ADV_SCAN_THREADS", "PUFF_ADV_RESERVE_SMS",
-                                                           "PUFF_ADV_TILE_ROWS", "PUFF_ADV_PDL", "PUFF_ADV_SCAN_WIDE"};
+                                                           "PUFF_ADV_TILE_ROWS", "PUFF_ADV_PDL", "PUFF_ADV_SCAN_WIDE",
+                                                           "PUFF_ADV_B1_WARP_TEAMS"};
         for (int i = 0; i < PUFF_TUNE_COUNT; ++i) {
             const char* v = getenv(names[i]);
             g_tune[i].store((v != nullptr && *v != '\0') ? atoi(v) : -1, std::memory_order_relaxed);
@@ -517,14 +519,29 @@ extern "C" int puff_advantage_sm100_launch_ex(const float* values, const float* 
             err = launch_kernel(puff_adv_bulk1d_ws_kernel, grid, kB1wThreads, ws_smem, st, values, rewards, dones,
                                 importance, advantages, seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments,
                                 static_cast<int>(horizon), ws_rows, tiles, zero_last);
+        } else if (horizon * 8 <= kB1WarpMaxElems && tune(PUFF_TUNE_B1_WARP_TEAMS, 1) != 0) {
+            // four warps per CTA, each on 8-row tiles of its own
+            const int teams = 4;
+            const int rows = 8;
+            const size_t arr = (static_cast<size_t>(rows) * horizon * 4 + 15) & ~static_cast<size_t>(15);
+            const size_t smem = teams * 4 * arr + 4 * 8 + 16 + 128;
+            const long long tiles = (num_segments + rows - 1) / rows;
+            const long long ctas = (tiles + teams - 1) / teams;
+            int per_sm = static_cast<int>(static_cast<size_t>(dev->max_smem_optin + 1024) / (smem + 1024));
+            per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+            const long long max_grid = static_cast<long long>(dev->sm_count) * per_sm;
+            const int grid = static_cast<int>(ctas < max_grid ? ctas : max_grid);
+            err = launch_kernel(puff_adv_bulk1d_kernel<32>, grid, kB1Threads, smem, st, values, rewards, dones, importance,
+                                advantages, seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments,
+                                static_cast<int>(horizon), rows, tiles, zero_last);
         } else {
         const long long tiles = (num_segments + bulk_rows - 1) / bulk_rows;
         int per_sm = static_cast<int>(static_cast<size_t>(dev->max_smem_optin + 1024) / (bulk_smem + 1024));
         per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
         const long long max_grid = static_cast<long long>(dev->sm_count) * per_sm;
         const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
-        err = launch_kernel(puff_adv_bulk1d_kernel, grid, kB1Threads, bulk_smem, st, values, rewards, dones, importance,
-                            advantages, seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments,
+        err = launch_kernel(puff_adv_bulk1d_kernel<kB1Threads>, grid, kB1Threads, bulk_smem, st, values, rewards, dones,
+                            importance, advantages, seg_abs_sum, gamma, lambda, rho_clip, c_clip, num_segments,
                             static_cast<int>(horizon), bulk_rows, tiles, zero_last);
         }
         g_launch_count.fetch_add(1, std::memory_order_relaxed);

@@ -24,7 +24,8 @@ def _clear_tuning():
     cabi.reset_tuning()
 
 
-def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=SENTINEL, stages=None, flags=0, ws=None):
+def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=SENTINEL, stages=None, flags=0, ws=None,
+            warp_teams=None):
     """Launch through the C ABI; returns (advantages, abs_sum or None, kernel name)."""
     from pufferlib_b200 import cabi
     from pufferlib_b200.advantage import launch_raw
@@ -32,7 +33,9 @@ def run_gpu(inputs, hyper, variant="auto", force=None, epilogue=False, sentinel=
     adv = torch.full_like(dev[0], sentinel)
     abs_sum = torch.full((dev[0].shape[0],), -1.0, device="cuda") if epilogue else None
     # ws: 0 = single-warp tma2d, N = warp-specialised with N stages
-    cabi.set_tuning(force_kernel=None if force is None else FORCE[force], stages=stages, ws_stages=ws)
+    # warp_teams: 0 = the one-stage bulk1d kernel with one tile per CTA, 1 (its default where it fits) one per warp
+    cabi.set_tuning(force_kernel=None if force is None else FORCE[force], stages=stages, ws_stages=ws,
+                    b1_warp_teams=warp_teams)
     try:
         launch_raw(*dev, adv, *hyper, seg_abs_sum=abs_sum, variant=variant, flags=flags)
         kernel = cabi.last_kernel()
@@ -520,15 +523,19 @@ def test_more_than_2_31_elements(H, force):
     torch.cuda.empty_cache()
 
 
-@pytest.mark.parametrize("ws", [0, 1])
-def test_bulk1d_forms(ws, golden_small):
-    """One-stage (0) and warp-specialised (1) forms of the odd-horizon kernel: golden
-    cases, ragged shapes, many tiles per CTA, literal path, fused sums, last column."""
+@pytest.mark.parametrize("ws,warp_teams", [(0, 1), (0, 0), (1, None)],
+                         ids=["one_stage_tile_per_warp", "one_stage_tile_per_cta", "pipeline"])
+def test_bulk1d_forms(ws, warp_teams, golden_small):
+    """The forms of the odd-horizon kernel -- one stage with a tile per warp (H <= 144) or per
+    CTA, and the warp-specialised pipeline: golden cases, ragged shapes, many tiles per CTA,
+    literal path, fused sums, last column."""
     from pufferlib_b200 import cabi
+    import functools
+    run = functools.partial(run_gpu, warp_teams=warp_teams)
     for name, case in golden_small.items():
         if case["values"].shape[1] < 2:
             continue
-        got, _, kernel = run_gpu([case[k] for k in KEYS], case["hyper"], "serial", "bulk1d", ws=ws)
+        got, _, kernel = run([case[k] for k in KEYS], case["hyper"], "serial", "bulk1d", ws=ws)
         assert kernel == "bulk1d"
         assert bits_equal(got, case["advantages"]), f"{name}/ws={ws}: {first_mismatch(got, case['advantages'])}"
     seed = 900
@@ -536,16 +543,16 @@ def test_bulk1d_forms(ws, golden_small):
         wl = Workload("b1", S, H, seed=seed, done_p=0.1)
         seed += 1
         inputs = [t.numpy() for t in make_inputs(wl)]
-        got, abs_sum, _ = run_gpu(inputs, wl.hyper(), "serial", "bulk1d", epilogue=True, ws=ws)
+        got, abs_sum, _ = run(inputs, wl.hyper(), "serial", "bulk1d", epilogue=True, ws=ws)
         want = oracle_advantage(inputs, wl.hyper())
         assert bits_equal(got, want), f"S={S} H={H} ws={ws}: {first_mismatch(got, want)}"
         exact = np.abs(want[:, :-1].astype(np.float64)).sum(1)
         np.testing.assert_allclose(abs_sum, exact, rtol=1e-5, atol=1e-6)
-        got0, _, _ = run_gpu(inputs, wl.hyper(), "serial", "bulk1d", ws=ws, flags=cabi.FLAG_ZERO_LAST_COLUMN)
+        got0, _, _ = run(inputs, wl.hyper(), "serial", "bulk1d", ws=ws, flags=cabi.FLAG_ZERO_LAST_COLUMN)
         assert bits_equal(got0, oracle_advantage(inputs, wl.hyper(), sentinel=0.0)), (S, H, ws)
     wl = Workload("b1frac", 500, 91, seed=77)
     v, r, d, w = [t.numpy() for t in make_inputs(wl)]
     d = np.random.default_rng(2).random(d.shape).astype(np.float32)
     want = oracle_advantage([v, r, d, w], wl.hyper())
-    got, _, _ = run_gpu([v, r, d, w], wl.hyper(), "serial", "bulk1d", ws=ws)
+    got, _, _ = run([v, r, d, w], wl.hyper(), "serial", "bulk1d", ws=ws)
     assert bits_equal(got, want), first_mismatch(got, want)
