@@ -52,7 +52,7 @@ from pufferlib_b200.workloads import WORKLOADS, make_inputs  # noqa: E402
 L2_BYTES = 126 * 1024 * 1024
 BYTES_PER_ELEMENT = 20          # 4 fp32 inputs read + 1 fp32 output written
 PRIO_ALPHA = 0.8                # config/default.ini:60
-DEPTH = 3                       # steps whose side-stream work may be outstanding
+DEPTH = int(os.environ.get("PUFF_BENCH_DEPTH", "3"))   # steps whose side-stream work may be outstanding
 FALLBACK_HBM_GBS = 6650.0
 
 
