@@ -453,6 +453,11 @@ def run_b200_arm(args, wl, rank, local_rank, world):
                 exchange.close()
                 exchange = None
                 exchange_kind = "torch.distributed all-reduce (NCCL); peer exchange unavailable on another rank"
+    elif os.environ.get("PUFF_BENCH_EXCHANGE_WORLD1") == "1":
+        # diagnosis: the exchange kernels (push into the own mailbox, gather from it) on one GPU
+        from pufferlib_b200.exchange import PeerExchange
+        exchange = PeerExchange(0, 1, want_handle=False)
+        exchange_kind = "peer-exchange kernels with a world of one (diagnosis)"
     if args.reserve_sms > 0:
         cabi.set_tuning(reserve_sms=args.reserve_sms)
 
